@@ -20,7 +20,7 @@ from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
 from .pool import Pool, PoolError
-from .spec import FixedState, PagedKV, PagedLatent, Several
+from .spec import FixedState, PagedKV, PagedLatent, Several, first_needed_position
 
 
 @dataclass
@@ -157,13 +157,14 @@ class CacheManager:
 
     def release_behind_window(self, request_id) -> int:
         """Give back the pages that no later query of the request can read.  The next query
-        sits at position num_tokens and reads from num_tokens - window + 1 on."""
+        sits at position num_tokens and reads from num_tokens - window + 1 on, and from the start of
+        its own block of `chunk` positions on."""
         rc = self.requests[request_id]
         freed = 0
         for need, pool, table in zip(self.layout.paged_groups, self.pools, rc.block_tables):
-            if need.window is None:
+            if need.window is None and not getattr(need, "chunk", None):
                 continue
-            first_needed = rc.num_tokens - need.window + 1
+            first_needed = first_needed_position(need, rc.num_tokens)
             dead_blocks = min(max(first_needed, 0) // self.page_size, len(table))
             gone = [table[b] for b in range(dead_blocks) if table[b] >= 0]
             for b in range(dead_blocks):

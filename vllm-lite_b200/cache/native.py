@@ -30,7 +30,7 @@ def _core():
         lib = build.load_host("cache_core")
         I, L, P, V = c_int, c_longlong, POINTER(c_int), c_void_p
         sig = {
-            "vc_create": (V, [I, I, P, P, I]), "vc_destroy": (None, [V]), "vc_admit": (I, [V, L, P]),
+            "vc_create": (V, [I, I, P, P, P, I]), "vc_destroy": (None, [V]), "vc_admit": (I, [V, L, P]),
             "vc_free": (I, [V, L]), "vc_has": (I, [V, L]), "vc_pages_needed": (I, [V, L, L, P]),
             "vc_append": (I, [V, L, L, POINTER(L)]), "vc_release_behind_window": (I, [V, L, P]),
             "vc_request_info": (I, [V, L, POINTER(L), P]), "vc_block_table": (I, [V, L, I, P, I]),
@@ -112,8 +112,9 @@ class NativeCacheManager:
         if any(n < 0 for n in counts):
             raise ValueError("a pool cannot have a negative size")
         windows = [int(g.window or 0) for g in layout.paged_groups]
+        chunks = [int(getattr(g, "chunk", None) or 0) for g in layout.paged_groups]
         arr = lambda v: (c_int * max(len(v), 1))(*v)
-        self._h = _core().vc_create(self.page_size, self.num_groups, arr(counts), arr(windows), int(max_requests))
+        self._h = _core().vc_create(self.page_size, self.num_groups, arr(counts), arr(windows), arr(chunks), int(max_requests))
         if not self._h:
             raise ValueError("the native cache core refused its sizes")
         self.pools = [_PoolView(self, g, "page") for g in range(self.num_groups)]

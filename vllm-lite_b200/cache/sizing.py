@@ -37,6 +37,12 @@ def _mixer_width(mixer) -> int:
     """Elements per token of a mixer's intermediates (float32 buffers count twice), a bound for the reserve."""
     if mixer is None:
         return 0
+    if hasattr(mixer, "inner"):                                         # a mixer behind a token shift: the mixed rows
+        return _mixer_width(mixer.inner) + getattr(mixer, "hidden_size", 0)
+    if hasattr(mixer, "conv") and hasattr(mixer, "num_kv_heads") and hasattr(mixer, "head_dim"):
+        # attention behind convolutions: the stacked projection, its convolved float32 copy, queries and context
+        hd = -(-mixer.head_dim // 16) * 16
+        return (mixer.num_heads + mixer.num_kv_heads) * mixer.head_dim * 3 + mixer.num_heads * (2 * hd + 1)
     if hasattr(mixer, "left") and hasattr(mixer, "right"):              # two mixers side by side, plus their sum
         return _mixer_width(mixer.left) + _mixer_width(mixer.right) + 2 * getattr(mixer.left, "hidden_size", 0)
     if hasattr(mixer, "num_kv_heads") and hasattr(mixer, "head_dim"):
@@ -105,6 +111,8 @@ def pages_from_memory(layout: CacheLayout, page_size: int, itemsize: int, free_b
         most = per_request
         if need.window is not None:
             most = min(most, -(-(need.window + (max_step_tokens or max_context)) // page_size) + 1)
+        if getattr(need, "chunk", None):
+            most = min(most, -(-(need.chunk + (max_step_tokens or max_context)) // page_size) + 1)
         least.append(most)                                    # what one request alone may come to hold
         caps.append(max_requests * most + 1)
     counts: List[Optional[int]] = [None] * len(costs)

@@ -2,7 +2,10 @@
 
 `PagedKV`: keys and values that grow by one row per token, stored in pages.
 `window`, when set, means that only the last `window` tokens are ever read, so
-pages that lie wholly before the window may be given back.
+pages that lie wholly before the window may be given back.  `chunk`, when set,
+means that positions form blocks of that many from the request's first token and
+no query reads a key of an earlier block, so pages that lie wholly before the
+block of the next query may be given back too.
 `PagedLatent`: one row per token from which keys and values are both derived (a
 compressed latent); paged and windowed like `PagedKV`, but stored once.
 `FixedState`: a tensor of fixed shape per request, stored in a slot.
@@ -22,6 +25,7 @@ class PagedKV:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    chunk: Optional[int] = None
 
     planes = 2                      # keys and values are stored apart
 
@@ -34,6 +38,7 @@ class PagedLatent:
     """A row of `width` numbers per token, read both as the key and as the value of one shared head."""
     width: int
     window: Optional[int] = None
+    chunk: Optional[int] = None
 
     planes = 1                      # one tensor serves as keys and as values
     num_kv_heads = 1
@@ -44,6 +49,16 @@ class PagedLatent:
 
     def bytes_per_token(self, itemsize: int) -> int:
         return self.width * itemsize
+
+
+def first_needed_position(need, num_tokens: int) -> int:
+    """The first position that a query at position `num_tokens` or later of a request can still read."""
+    first = 0
+    if need.window is not None:
+        first = max(first, num_tokens - need.window + 1)
+    if getattr(need, "chunk", None):
+        first = max(first, num_tokens // need.chunk * need.chunk)
+    return first
 
 
 @dataclass(frozen=True)

@@ -6,3 +6,4 @@ from .registry import (ArchitectureEntry, plan_from_config_json, register_archit
 from . import qwen3_plan as _qwen3_plan  # noqa: F401  (registers Qwen3ForCausalLM)
 from .kikepel import KikepelConfig  # noqa: F401,E402  (registers Kikepel)
 from .tuzisun import TuzisunConfig  # noqa: F401,E402  (registers Tuzisun)
+from .sodonex import SodonexConfig  # noqa: F401,E402  (registers Sodonex)

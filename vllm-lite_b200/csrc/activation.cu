@@ -134,6 +134,29 @@ extern "C" int vl_gated_act(const void* gu, void* out, int dtype, int T, int I, 
     return VL_ERR_UNSUPPORTED;
 }
 
+// A function of one argument, element by element in float32: act 16 = the square of max(v, 0) (the codes continue
+// those of the gated activations, which take two).
+template <typename T>
+__global__ void unary_act_kernel(const T* __restrict__ in, T* __restrict__ out, size_t n, int act) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= n) return;
+    float v = to_f32(in[i]);
+    if (act == 16) { v = fmaxf(v, 0.f); v = v * v; }
+    out[i] = from_f32<T>(v);
+}
+
+extern "C" int vl_unary_act(const void* in, void* out, int dtype, long long n, int act, void* stream) {
+    if (n <= 0) return VL_OK;
+    if (act != 16) return VL_ERR_ARGUMENT;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VL_F32) return vl_launch(unary_act_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)in, (float*)out, (size_t)n, act);
+    if (dtype == VL_BF16) return vl_launch(unary_act_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (const bf16*)in, (bf16*)out, (size_t)n, act);
+    return VL_ERR_UNSUPPORTED;
+}
+
 // Logits of a scaled, capped output head, in place on float32:  z <- cap * tanh(z * scale / cap)
 // (cap <= 0: only the scale).
 __global__ void scale_softcap_kernel(float* __restrict__ z, size_t n, float scale, float cap) {

@@ -9,6 +9,10 @@
 // (crates/model/src/components/attention/util.rs:150-176 of the reference;
 //  query head h reads KV head h / (nq / nkv), util.rs:55-87).
 // Scores, the running maximum, the sum and the output are float32.
+// Options of every mode: `chunk` > 0 cuts the positions into blocks of that many, counted from a request's first
+// token, and a query reads no key of an earlier block (lo is then at least the start of the query's block); `gate`
+// multiplies head h's output for token t by sigmoid(gate[t * gate_stride + h]).  Weighting ATT_SIGMOID replaces the
+// softmax: every visible key weighs sigmoid(s_j + head_bias[h]) by itself and nothing is divided by a sum.
 //
 // vl_paged_attention: one block per (token, query head), 16 groups of 8 lanes.
 // Group g owns the keys whose position is g modulo 16 and keeps a running
@@ -32,14 +36,18 @@ template <> struct Pair<bf16> {
     }
 };
 
-template <typename T, int R>
+#define ATT_SOFTMAX 0
+#define ATT_SIGMOID 1
+
+template <typename T, int R, int MODE>
 __global__ void __launch_bounds__(ATT_THREADS)
 paged_attention_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out,
                        const T* __restrict__ kcache, const T* __restrict__ vcache,
                        const int* __restrict__ block_table, int max_blocks,
                        const int* __restrict__ req_index, const int* __restrict__ positions,
                        int nq, int nkv, int page_size, int num_pages, float scale, int window,
-                       const float* __restrict__ sinks, unsigned* err) {
+                       const float* __restrict__ sinks, int chunk, const float* __restrict__ head_bias,
+                       const T* __restrict__ gate, int gate_stride, unsigned* err) {
     constexpr int HD = R * 16;
     __shared__ float s_acc[ATT_GROUPS][HD];
     __shared__ float s_m[ATT_GROUPS], s_l[ATT_GROUPS];
@@ -48,8 +56,10 @@ paged_attention_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
     const int g = threadIdx.x >> 3, l = threadIdx.x & 7;
     const int req = req_index[t];
     const int pos = positions[t];
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    if (chunk > 0 && pos >= 0) lo = max(lo, pos / chunk * chunk);
     const int* table = block_table + (size_t)req * max_blocks;
+    const float hb = (MODE == ATT_SIGMOID && head_bias) ? head_bias[h] : 0.f;
 
     float qr[R][2], acc[R][2];
     const T* qp = q + (size_t)t * q_stride + (size_t)h * HD;
@@ -88,7 +98,16 @@ paged_attention_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
         dot += __shfl_xor_sync(0xffffffffu, dot, 4);
         dot += __shfl_xor_sync(0xffffffffu, dot, 2);
         dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-        if (valid) {
+        if (valid && MODE == ATT_SIGMOID) {
+            const float p = 1.0f / (1.0f + expf(-(dot * scale + hb)));
+            const T* vp = vcache + base;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const float2 vv = Pair<T>::load(vp + 16 * r + 2 * l);
+                acc[r][0] += p * vv.x;
+                acc[r][1] += p * vv.y;
+            }
+        } else if (valid) {
             const float s = dot * scale;
             const float mn = fmaxf(m, s);
             const float corr = expf(m - mn);
@@ -111,6 +130,17 @@ paged_attention_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
     }
     if (l == 0) { s_m[g] = m; s_l[g] = lsum; }
     __syncthreads();
+    const float gt = gate ? 1.0f / (1.0f + expf(-to_f32(gate[(size_t)t * gate_stride + h]))) : 1.0f;
+    if (MODE == ATT_SIGMOID) {                                   // the groups' sums, added in group order
+        T* op = out + ((size_t)t * nq + h) * HD;
+        for (int e = threadIdx.x; e < HD; e += ATT_THREADS) {
+            float o = 0.f;
+#pragma unroll
+            for (int i = 0; i < ATT_GROUPS; ++i) o += s_acc[i][e];
+            op[e] = from_f32<T>(gate ? o * gt : o);
+        }
+        return;
+    }
     float M = -INFINITY;
 #pragma unroll
     for (int i = 0; i < ATT_GROUPS; ++i) M = fmaxf(M, s_m[i]);
@@ -127,7 +157,8 @@ paged_attention_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
             o += s_acc[i][e] * wgt;
         }
         if (sinks) L += expf(sink - M);
-        op[e] = from_f32<T>(L > 0.f ? o / L : 0.f);
+        const float res = L > 0.f ? o / L : 0.f;
+        op[e] = from_f32<T>(gate ? res * gt : res);
     }
 }
 
@@ -135,12 +166,18 @@ template <typename T>
 static int launch_paged_attention(int R, dim3 grid, cudaStream_t s, const T* q, int q_stride, T* out,
                                   const T* kc, const T* vc, const int* bt, int max_blocks,
                                   const int* req, const int* pos, int nq, int nkv, int page_size,
-                                  int num_pages, float scale, int window, const float* sinks, unsigned* err) {
+                                  int num_pages, float scale, int window, const float* sinks, int mode, int chunk,
+                                  const float* head_bias, const T* gate, int gate_stride, unsigned* err) {
 #define ATT_CASE(RR)                                                                              \
     case RR:                                                                                      \
-        paged_attention_kernel<T, RR><<<grid, ATT_THREADS, 0, s>>>(                               \
-            q, q_stride, out, kc, vc, bt, max_blocks, req, pos, nq, nkv, page_size, num_pages,    \
-            scale, window, sinks, err);                                                           \
+        if (mode == ATT_SIGMOID)                                                                  \
+            paged_attention_kernel<T, RR, ATT_SIGMOID><<<grid, ATT_THREADS, 0, s>>>(              \
+                q, q_stride, out, kc, vc, bt, max_blocks, req, pos, nq, nkv, page_size, num_pages,\
+                scale, window, sinks, chunk, head_bias, gate, gate_stride, err);                  \
+        else                                                                                      \
+            paged_attention_kernel<T, RR, ATT_SOFTMAX><<<grid, ATT_THREADS, 0, s>>>(              \
+                q, q_stride, out, kc, vc, bt, max_blocks, req, pos, nq, nkv, page_size, num_pages,\
+                scale, window, sinks, chunk, head_bias, gate, gate_stride, err);                  \
         break;
     switch (R) {
         ATT_CASE(1) ATT_CASE(2) ATT_CASE(3) ATT_CASE(4) ATT_CASE(5) ATT_CASE(6) ATT_CASE(7) ATT_CASE(8)
@@ -156,10 +193,13 @@ extern "C" int vl_paged_attention(const void* q, int q_stride, void* out, int dt
                                   const int* block_table, int max_blocks,
                                   const int* req_index, const int* positions,
                                   int T, int nq, int nkv, int hd, int page_size, int num_pages,
-                                  float scale, int window, const float* sinks, unsigned* err, void* stream) {
+                                  float scale, int window, const float* sinks, int mode, int chunk,
+                                  const float* head_bias, const void* gate, int gate_stride, unsigned* err, void* stream) {
     if (T <= 0) return VL_OK;
     if (hd <= 0 || hd % 16 || hd > ATT_MAX_HD) return VL_ERR_UNSUPPORTED;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0) return VL_ERR_ARGUMENT;
+    if ((mode != ATT_SOFTMAX && mode != ATT_SIGMOID) || chunk < 0 || (mode == ATT_SIGMOID && sinks)) return VL_ERR_ARGUMENT;
+    if (gate && gate_stride < nq) return VL_ERR_ARGUMENT;
     if (nq > 65535) return VL_ERR_UNSUPPORTED;
     dim3 grid(T, nq);
     cudaStream_t s = (cudaStream_t)stream;
@@ -167,12 +207,14 @@ extern "C" int vl_paged_attention(const void* q, int q_stride, void* out, int dt
         return launch_paged_attention<float>(hd / 16, grid, s, (const float*)q, q_stride, (float*)out,
                                              (const float*)kcache, (const float*)vcache, block_table,
                                              max_blocks, req_index, positions, nq, nkv, page_size,
-                                             num_pages, scale, window, sinks, err);
+                                             num_pages, scale, window, sinks, mode, chunk, head_bias,
+                                             (const float*)gate, gate_stride, err);
     if (dtype == VL_BF16)
         return launch_paged_attention<bf16>(hd / 16, grid, s, (const bf16*)q, q_stride, (bf16*)out,
                                             (const bf16*)kcache, (const bf16*)vcache, block_table,
                                             max_blocks, req_index, positions, nq, nkv, page_size,
-                                            num_pages, scale, window, sinks, err);
+                                            num_pages, scale, window, sinks, mode, chunk, head_bias,
+                                            (const bf16*)gate, gate_stride, err);
     return VL_ERR_UNSUPPORTED;
 }
 

@@ -11,7 +11,7 @@
 
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
-                             float* __restrict__ x, int H, int V, unsigned* err) {
+                             float* __restrict__ x, int H, int V, float scale, unsigned* err) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -23,7 +23,7 @@ __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__
         return;
     }
     const TW* src = table + (size_t)id * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) row[i] = to_f32(src[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) row[i] = to_f32(src[i]) * scale;   // float32; times 1 is exact
 }
 
 // rows == nullptr: row r of the output is row r of x (and x is updated in place
@@ -281,14 +281,93 @@ extern "C" int vl_layernorm_rows(const float* x, const int* rows, const float* w
     return VL_ERR_UNSUPPORTED;
 }
 
+// RMS norm of a sub-layer's OUTPUT added into the stream with a factor: x[r] += mult * (y[r] / sqrt(mean(y[r]^2) + eps) * w)
+// (y in the activation dtype, x the float32 stream, everything between in float32) and, when asked, cast[r] = x[r] in
+// the activation dtype: the next sub-layer's input.  The row of y is kept in registers where it fits (H a multiple of
+// 4, at most 256 * 4 * VPT values), else read twice.  The order of the sums depends on the row length alone.
+template <typename TA>
+__global__ void __launch_bounds__(256)
+rmsnorm_add_kernel(const TA* __restrict__ y, const float* __restrict__ w, float eps, float mult, float* __restrict__ x,
+                   TA* __restrict__ cast, int H) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const TA* yr = y + (size_t)r * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += 256) { const float d = to_f32(yr[i]); ss += d * d; }
+    const float inv = 1.0f / sqrtf(block_sum<256>(ss, scratch) / (float)H + eps);
+    float* xr = x + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += 256) {
+        const float v = xr[i] + mult * (to_f32(yr[i]) * inv * w[i]);
+        xr[i] = v;
+        if (cast) cast[(size_t)r * H + i] = from_f32<TA>(v);
+    }
+}
+
+template <typename TA, int VPT>
+__global__ void __launch_bounds__(256)
+rmsnorm_add_vec_kernel(const TA* __restrict__ y, const float* __restrict__ w, float eps, float mult, float* __restrict__ x,
+                       TA* __restrict__ cast, int H) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x, H4 = H >> 2;
+    const TA* yr = y + (size_t)r * H;
+    float4 v[VPT];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + 256 * i;
+        if (c < H4) {
+            v[i] = Quad<TA>::load(yr + 4 * c);
+            ss += v[i].x * v[i].x; ss += v[i].y * v[i].y; ss += v[i].z * v[i].z; ss += v[i].w * v[i].w;
+        }
+    }
+    const float inv = 1.0f / sqrtf(block_sum<256>(ss, scratch) / (float)H + eps);
+    float* xr = x + (size_t)r * H;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + 256 * i;
+        if (c < H4) {
+            const float4 g = Quad<float>::load(w + 4 * c);
+            float4 o = Quad<float>::load(xr + 4 * c);
+            o.x += mult * (v[i].x * inv * g.x); o.y += mult * (v[i].y * inv * g.y);
+            o.z += mult * (v[i].z * inv * g.z); o.w += mult * (v[i].w * inv * g.w);
+            Quad<float>::store(xr + 4 * c, o);
+            if (cast) Quad<TA>::store(cast + (size_t)r * H + 4 * c, o);
+        }
+    }
+}
+
+template <typename TA>
+static int launch_rmsnorm_add(const TA* y, const float* w, float eps, float mult, float* x, TA* cast, int R, int H, cudaStream_t s) {
+    const int pieces = (H / 4 + 255) / 256;
+    if (H % 4 == 0 && pieces <= 1) return vl_launch(rmsnorm_add_vec_kernel<TA, 1>, dim3(R), dim3(256), 0, s, y, w, eps, mult, x, cast, H);
+    if (H % 4 == 0 && pieces <= 2) return vl_launch(rmsnorm_add_vec_kernel<TA, 2>, dim3(R), dim3(256), 0, s, y, w, eps, mult, x, cast, H);
+    if (H % 4 == 0 && pieces <= 4) return vl_launch(rmsnorm_add_vec_kernel<TA, 4>, dim3(R), dim3(256), 0, s, y, w, eps, mult, x, cast, H);
+    if (H % 4 == 0 && pieces <= 8) return vl_launch(rmsnorm_add_vec_kernel<TA, 8>, dim3(R), dim3(256), 0, s, y, w, eps, mult, x, cast, H);
+    return vl_launch(rmsnorm_add_kernel<TA>, dim3(R), dim3(256), 0, s, y, w, eps, mult, x, cast, H);
+}
+
+extern "C" int vl_rmsnorm_add(const void* y, int act_dtype, const float* w, float eps, float mult, float* x, void* cast,
+                              int R, int H, void* stream) {
+    if (R <= 0) return VL_OK;
+    if (H <= 0) return VL_ERR_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == VL_F32) return launch_rmsnorm_add<float>((const float*)y, w, eps, mult, x, (float*)cast, R, H, s);
+    if (act_dtype == VL_BF16) return launch_rmsnorm_add<bf16>((const bf16*)y, w, eps, mult, x, (bf16*)cast, R, H, s);
+    return VL_ERR_UNSUPPORTED;
+}
+
 extern "C" int vl_embed(const int* ids, const void* table, int table_dtype, float* x,
-                        int T, int H, int V, unsigned* err, void* stream) {
+                        int T, int H, int V, float scale, unsigned* err, void* stream) {
     if (T <= 0) return VL_OK;
     cudaStream_t s = (cudaStream_t)stream;
     if (table_dtype == VL_F32)
-        vl_launch(embed_kernel<float>, dim3(T), dim3(256), 0, s, ids, (const float*)table, x, H, V, err);
+        vl_launch(embed_kernel<float>, dim3(T), dim3(256), 0, s, ids, (const float*)table, x, H, V, scale, err);
     else if (table_dtype == VL_BF16)
-        vl_launch(embed_kernel<bf16>, dim3(T), dim3(256), 0, s, ids, (const bf16*)table, x, H, V, err);
+        vl_launch(embed_kernel<bf16>, dim3(T), dim3(256), 0, s, ids, (const bf16*)table, x, H, V, scale, err);
     else
         return VL_ERR_UNSUPPORTED;
     return vl_launch_status();

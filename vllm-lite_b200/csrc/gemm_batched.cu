@@ -101,6 +101,8 @@ gemm_batched_nt_kernel(const T* __restrict__ A, const TW* __restrict__ W, TC* __
 //              (W (s a) = s (W a): the expert weight on the input, applied to the exact sums);
 //   act        W holds blocks of 8 gate rows and their 8 up rows (as the dense products' fused SwiGLU);
 //              the tile applies the gated activation (activation.cu's formulas) and writes N / 2 columns.
+//              act >= GM_ACT_UNARY: W is a plain matrix and the tile applies a function of one argument to its
+//              N columns (GM_ACT_UNARY + 0: the square of max(v, 0)).
 // Every output element is summed over K in steps of 16 in order, whatever its place in the tile.
 // ---------------------------------------------------------------------------------------------------
 #define GM_BN 64
@@ -108,6 +110,11 @@ gemm_batched_nt_kernel(const T* __restrict__ A, const TW* __restrict__ W, TC* __
 #define GM_LDS 72
 #define GM_NST 4
 #define GM_ACT_NONE (-1)
+#define GM_ACT_UNARY 16
+__device__ __forceinline__ float gm_unary(float v, int act) {
+    if (act == GM_ACT_UNARY) { v = fmaxf(v, 0.f); return v * v; }
+    return v;
+}
 
 __device__ __forceinline__ void gm_cp_async16(void* smem, const void* gmem, bool valid) {
     const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
@@ -231,11 +238,11 @@ gemm_batched_bf16_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict_
             scale = p >= 0 ? row_scale[p] : 0.f;
         }
         TC* crow = Cb + (size_t)m * ldc;
-        if (act == GM_ACT_NONE) {
+        if (act == GM_ACT_NONE || act >= GM_ACT_UNARY) {
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 const int n = n0 + wn * WN + nt * 8 + t2;
-                const float v0 = acc[nt][2 * half] * scale, v1 = acc[nt][2 * half + 1] * scale;
+                const float v0 = gm_unary(acc[nt][2 * half] * scale, act), v1 = gm_unary(acc[nt][2 * half + 1] * scale, act);
                 if (sizeof(TC) == 2 && pair_ok && n + 1 < N) {          // two bfloat16 in one 4-byte store
                     __nv_bfloat162 pr = __floats2bfloat162_rn(v0, v1);
                     *reinterpret_cast<unsigned*>(crow + n) = *reinterpret_cast<unsigned*>(&pr);
@@ -358,7 +365,7 @@ extern "C" int vl_gemm_rows_f32w(const void* A, int a_dtype, const void* W, int 
 
 // 1 when `vl_gemm_grouped_fused` takes these sizes (bfloat16 only): rows of A and W on 16-byte boundaries.
 extern "C" int vl_gemm_grouped_fused_ok(int K, int N, int act) {
-    return K % 8 == 0 && (act == GM_ACT_NONE || N % 16 == 0) && !vl_batched_simt_only();
+    return K % 8 == 0 && (act == GM_ACT_NONE || act >= GM_ACT_UNARY || N % 16 == 0) && !vl_batched_simt_only();
 }
 
 // The grouped product of a routed feed-forward with its neighbours folded in (bfloat16, tensor cores):
@@ -370,7 +377,8 @@ extern "C" int vl_gemm_grouped_fused(const void* A, const void* W, void* C, int 
                                      const float* row_scale, int act, float alpha, float limit, float shift, void* stream) {
     if (M <= 0 || N <= 0) return VL_OK;
     if (K <= 0 || lda < K || (bm != 64 && bm != 16) || M % bm || !tile_group || index_div <= 0) return VL_ERR_ARGUMENT;
-    if (act < GM_ACT_NONE || act > 2 || ldc < (act == GM_ACT_NONE ? N : N / 2)) return VL_ERR_ARGUMENT;
+    const bool gated = act >= 0 && act < GM_ACT_UNARY;
+    if (act < GM_ACT_NONE || (act > 2 && act != GM_ACT_UNARY) || ldc < (gated ? N / 2 : N)) return VL_ERR_ARGUMENT;
     if (!vl_gemm_grouped_fused_ok(K, N, act) || !gm_aligned(A, W, K, lda, K, 0, 0, w_gs)) return VL_ERR_UNSUPPORTED;
     return launch_batched_mma((const bf16*)A, (const bf16*)W, (bf16*)C, M, N, K, lda, K, ldc, 0, 0, 0, 1, tile_group, w_gs, bm,
                               row_index, index_div, row_scale, act, alpha, limit, shift, (cudaStream_t)stream);

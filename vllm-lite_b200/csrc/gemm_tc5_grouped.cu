@@ -7,7 +7,8 @@
 // the next group; their columns are never stored.
 // The epilogue can do what a routed feed-forward needs around its first product: multiply the float32
 // sums of row m by row_scale[row_index[m]] (the expert weight on the input: W (s a) = s (W a)), and
-// apply the gated activation to blocks of 8 gate and 8 up columns (act >= 0: C is [M, N / 2]).
+// apply the gated activation to blocks of 8 gate and 8 up columns (act 0..2: C is [M, N / 2]) or, act 16, the
+// square of max(v, 0) to every column of a plain W.
 // Roles, stages, tensor memory and the bounded waits are those of csrc/gemm_tc5.cu.
 #include "tc5.cuh"
 
@@ -166,7 +167,14 @@ gemm_tc5_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * scale);
                 }
-                if (act < 0) {
+                if (act < 0 || act >= 16) {
+                    if (act == 16) {                         // a function of one argument: the square of max(v, 0)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const float f = fmaxf(__uint_as_float(v[i]), 0.f);
+                            v[i] = __float_as_uint(f * f);
+                        }
+                    }
                     store_chunk32<TO>(v, C + (size_t)row * ldc, n0 + c0, N, 0);
                 } else {
                     // two blocks of 8 gate and 8 up columns become 16 columns of C at col / 2
@@ -229,11 +237,12 @@ extern "C" int vl_gemm_bf16_tc5_grouped(const void* A, const void* W, void* C, i
                                         int act, float alpha, float limit, float shift, unsigned* err, void* stream) {
     if (M <= 0 || N <= 0) return VL_OK;
     if (K <= 0 || K % 8 || G <= 0 || M % BM || !tile_group) return VL_ERR_UNSUPPORTED;
-    if (act < -1 || act > 2 || (act >= 0 && N % 16)) return VL_ERR_ARGUMENT;
+    const bool gated = act >= 0 && act < 16;                 // 16: a function of one argument on a plain W
+    if (act < -1 || (act > 2 && act != 16) || (gated && N % 16)) return VL_ERR_ARGUMENT;
     if ((long long)G * N >= (1ll << 31)) return VL_ERR_UNSUPPORTED;
     if (((uintptr_t)A | (uintptr_t)W) & 15) return VL_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    const int ldc = act >= 0 ? N / 2 : N;
+    const int ldc = gated ? N / 2 : N;
     if (N > 128) return launch_grouped<256, 4>(A, W, (bf16*)C, M, N, K, G, ldc, err, tile_group, row_index, row_scale, act, alpha,
                                                limit, shift, s);
     return launch_grouped<128, 6>(A, W, (bf16*)C, M, N, K, G, ldc, err, tile_group, row_index, row_scale, act, alpha, limit,

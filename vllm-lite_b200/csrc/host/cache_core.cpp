@@ -70,6 +70,7 @@ struct Core {
     int page_size = 16;
     std::vector<Pool> pools;
     std::vector<int> windows;                 // per group, 0 = none
+    std::vector<int> chunks;                  // per group, 0 = none: positions in blocks of that many, no key of an earlier block is read
     Pool slots;
     std::unordered_map<long long, Request> requests;
     std::vector<int> fresh_slots;
@@ -87,7 +88,8 @@ inline int align4(int n) { return (n + 3) & ~3; }
 
 extern "C" {
 
-void* vc_create(int page_size, int num_groups, const int* pages_per_group, const int* windows, int max_requests) {
+void* vc_create(int page_size, int num_groups, const int* pages_per_group, const int* windows, const int* chunks,
+                int max_requests) {
     if (page_size <= 0 || num_groups < 0 || max_requests < 0) return nullptr;
     Core* c = new Core();
     c->page_size = page_size;
@@ -95,6 +97,7 @@ void* vc_create(int page_size, int num_groups, const int* pages_per_group, const
         if (pages_per_group[g] < 0) { delete c; return nullptr; }
         c->pools.emplace_back(pages_per_group[g]);
         c->windows.push_back(windows ? windows[g] : 0);
+        c->chunks.push_back(chunks ? chunks[g] : 0);
     }
     c->slots = Pool(max_requests);
     return c;
@@ -162,7 +165,8 @@ int vc_append(void* h, long long key, long long count, long long* start) {
 }
 
 // Gives back the pages that no later query of the request can read: the next query sits at
-// position num_tokens and reads from num_tokens - window + 1 on.  *freed = pages returned.
+// position num_tokens and reads from num_tokens - window + 1 on, and from the start of its own block of
+// `chunk` positions on.  *freed = pages returned.
 int vc_release_behind_window(void* h, long long key, int* freed) {
     Core* c = static_cast<Core*>(h);
     auto it = c->requests.find(key);
@@ -170,10 +174,11 @@ int vc_release_behind_window(void* h, long long key, int* freed) {
     Request& r = it->second;
     int total = 0;
     for (size_t g = 0; g < c->pools.size(); ++g) {
-        const int w = c->windows[g];
-        if (w <= 0) continue;
-        long long first_needed = r.num_tokens - w + 1;
+        const int w = c->windows[g], ch = c->chunks[g];
+        if (w <= 0 && ch <= 0) continue;
+        long long first_needed = w > 0 ? r.num_tokens - w + 1 : 0;
         if (first_needed < 0) first_needed = 0;
+        if (ch > 0 && r.num_tokens / ch * ch > first_needed) first_needed = r.num_tokens / ch * ch;
         long long dead = first_needed / c->page_size;
         if (dead > (long long)r.tables[g].size()) dead = (long long)r.tables[g].size();
         std::vector<int> gone;

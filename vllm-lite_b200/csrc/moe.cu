@@ -2,7 +2,7 @@
 // experts' results back together.  The products themselves are the grouped form of
 // gemm_batched.cu, the experts' activation is in activation.cu.
 //
-//   vl_moe_route    from the logits z = W_r h (float32, a product of csrc/gemm_batched.cu): score =
+//   vl_moe_route    from the logits z = W_r h (+ bias) (float32, a product of csrc/gemm_batched.cu): score =
 //                   sigmoid(z) or softmax(z); the `top` largest pick the experts of a token (ties: the
 //                   lower index), weights = the scores as they are or divided by their sum.
 //                   -> expert ids [T, top], weights float32 [T, top]
@@ -26,7 +26,8 @@
 // one warp per token; z [ntok, E]: the router's logits (csrc/gemm_batched.cu: vl_gemm_rows_f32w)
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ z, int slices, int ntok, int E, int top,
-                 int score_fn, int renorm, int groups, int keep, int* __restrict__ ids, float* __restrict__ weights) {
+                 int score_fn, int renorm, int groups, int keep, const float* __restrict__ bias,
+                 int* __restrict__ ids, float* __restrict__ weights) {
     extern __shared__ float s_scores[];                  // [4][E], then [4][groups] when the experts form groups
     pdl_launch_dependents();
     pdl_wait();
@@ -37,7 +38,7 @@ moe_route_kernel(const float* __restrict__ z, int slices, int ntok, int E, int t
     for (int e = lane; e < E; e += 32) {                 // the logits came as sums over slices of K: added in their order
         float v = 0.f;
         for (int sl = 0; sl < slices; ++sl) v += z[((size_t)sl * ntok + t) * E + e];
-        sc[e] = v;
+        sc[e] = bias ? v + bias[e] : v;
     }
     __syncwarp();
     // The choice is made on the logits: both score functions grow with z, and a sigmoid that has
@@ -198,13 +199,13 @@ __global__ void moe_combine_kernel(const T* __restrict__ result, const int* __re
 }
 
 extern "C" int vl_moe_route(const float* z, int slices, int T, int E, int top, int score_fn, int renorm, int groups, int keep,
-                            int* ids, float* weights, void* stream) {
+                            const float* bias, int* ids, float* weights, void* stream) {
     if (T <= 0) return VL_OK;
     if (E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > E || slices <= 0) return VL_ERR_ARGUMENT;
     if (score_fn != MOE_SCORE_SIGMOID && score_fn != MOE_SCORE_SOFTMAX) return VL_ERR_ARGUMENT;
     if (groups < 1 || E % groups || keep < 1 || keep > groups || keep * (E / groups) < top) return VL_ERR_ARGUMENT;
     return vl_launch(moe_route_kernel, dim3((T + 3) / 4), dim3(128), (size_t)4 * (E + groups) * sizeof(float),
-                     (cudaStream_t)stream, z, slices, T, E, top, score_fn, renorm, groups, keep, ids, weights);
+                     (cudaStream_t)stream, z, slices, T, E, top, score_fn, renorm, groups, keep, bias, ids, weights);
 }
 
 // cap = rows of the sorted buffer (a multiple of bm, at least npairs rounded up per expert: npairs + E * (bm - 1)

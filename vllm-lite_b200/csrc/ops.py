@@ -32,7 +32,8 @@ def dtype_code(dtype) -> int:
 
 
 _SIGNATURES = {
-    ("embed_norm", "vl_embed"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    ("embed_norm", "vl_embed"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+    ("embed_norm", "vl_rmsnorm_add"): [c_void_p, c_int, c_void_p, c_float, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p],
     ("embed_norm", "vl_add_rmsnorm"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     ("embed_norm", "vl_add_bias"): [c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p],
     ("embed_norm", "vl_cast"): [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p],
@@ -41,7 +42,13 @@ _SIGNATURES = {
                                               c_void_p, c_void_p],
     ("attention", "vl_paged_attention"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                          c_float, c_int, c_void_p, c_void_p, c_void_p],
+                                          c_float, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+    ("rope_cache", "vl_rows_norm_rope_write"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int,
+                                                c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                c_longlong, c_void_p, c_void_p],
+    ("recurrent", "vl_token_shift"): [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_int, c_int, c_int, c_void_p],
+    ("activation", "vl_unary_act"): [c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p],
     ("attention", "vl_decode_attention"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                            c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -75,7 +82,8 @@ _SIGNATURES = {
     ("gemm_batched", "vl_gemm_grouped_fused"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                                 c_longlong, c_int, c_void_p, c_int, c_void_p, c_int, c_float, c_float, c_float,
                                                 c_void_p],
-    ("moe", "vl_moe_route"): [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    ("moe", "vl_moe_route"): [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                              c_void_p],
     ("gemm_batched", "vl_gemm_rows_f32w"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     ("gemm_tc5_grouped", "vl_gemm_bf16_tc5_grouped"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                                        c_void_p, c_int, c_float, c_float, c_float, c_void_p, c_void_p],
@@ -180,14 +188,14 @@ def _need(t, dtype, name, ndim=None):
 
 
 # ---------------------------------------------------------------- embed / norm
-def embed(ids, table, out, err):
-    """out[t, :] = table[ids[t], :] as float32.  ids int32 [T]; out float32 [T, H]."""
+def embed(ids, table, out, err, scale=1.0):
+    """out[t, :] = table[ids[t], :] * scale as float32.  ids int32 [T]; out float32 [T, H]."""
     _need(ids, torch.int32, "ids", 1); _need(table, None, "table", 2); _need(out, torch.float32, "out", 2)
     T, (V, H) = ids.shape[0], table.shape
     if out.shape != (T, H):
         raise KernelError(f"out must be [{T}, {H}], got {tuple(out.shape)}")
     _check(_fn("embed_norm", "vl_embed")(_ptr(ids), _ptr(table), dtype_code(table.dtype), _ptr(out), T, H, V,
-                                         _ptr(err), _stream()), "vl_embed")
+                                         float(scale), _ptr(err), _stream()), "vl_embed")
     return out
 
 
@@ -262,6 +270,57 @@ def qk_norm_rope_write(qkv, positions, slots, q_weight, k_weight, eps, inv_freq,
     return qkv
 
 
+def rows_norm_rope_write(qk, positions, slots, q_weight, k_weight, eps, inv_freq, rotary_dim, q_out,
+                         k_cache, v_cache, num_heads, num_kv_heads, head_dim, err, padded_head_dim=None):
+    """qk float32 [T, >= (nq + nkv) hd] = q | k.  v <- k as it is; q and k are divided by the root mean square of their
+    WHOLE row part (all heads at once) and multiplied by q_weight [nq hd] / k_weight [nkv hd]; then the first
+    `rotary_dim` features of every head turn by the position; q goes to q_out [T, nq hdp], k and v to the cache
+    [pages, nkv, page_size, hdp] at `slots` (None or negative: no write).  hdp = `padded_head_dim` (default hd) is the
+    head size of the outputs; the features from hd on are zeros."""
+    _need(qk, torch.float32, "qk", 2); _need(positions, torch.int32, "positions", 1); _need(q_out, None, "q_out", 2)
+    _need(q_weight, torch.float32, "q_weight", 1); _need(k_weight, torch.float32, "k_weight", 1)
+    T = qk.shape[0]
+    Cq, Ck = num_heads * head_dim, num_kv_heads * head_dim
+    hdp = int(padded_head_dim or head_dim)
+    if qk.shape[1] < Cq + Ck or positions.shape[0] != T or q_out.shape != (T, num_heads * hdp) or q_weight.shape[0] != Cq \
+            or k_weight.shape[0] != Ck:
+        raise KernelError(f"rows_norm_rope_write: qk {tuple(qk.shape)}, q_out {tuple(q_out.shape)}, heads {num_heads}+{num_kv_heads} x {head_dim}")
+    page_size, num_slots = 1, 0
+    if slots is not None:
+        _need(slots, torch.int32, "slots", 1)
+        _need(k_cache, q_out.dtype, "k_cache", 4); _need(v_cache, q_out.dtype, "v_cache", 4)
+        if k_cache.shape != v_cache.shape or k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != hdp:
+            raise KernelError(f"cache {tuple(k_cache.shape)} does not match kv heads {num_kv_heads} x {hdp}")
+        page_size = k_cache.shape[2]
+        num_slots = k_cache.shape[0] * page_size
+    if inv_freq is not None:
+        _need(inv_freq, torch.float32, "inv_freq", 1)
+        if inv_freq.shape[0] * 2 != rotary_dim:
+            raise KernelError("inv_freq must have rotary_dim / 2 entries")
+    _check(_fn("rope_cache", "vl_rows_norm_rope_write")(
+        _ptr(qk), qk.shape[1], _ptr(positions), _ptr(slots), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(inv_freq),
+        int(rotary_dim if inv_freq is not None else 0), _ptr(q_out), dtype_code(q_out.dtype),
+        _ptr(k_cache) if slots is not None else None, _ptr(v_cache) if slots is not None else None, T, num_heads,
+        num_kv_heads, head_dim, hdp, page_size, num_slots, _ptr(err), _stream()), "vl_rows_norm_rope_write")
+    return q_out
+
+
+def token_shift(x, mu, state, state_off, cu, slots, req_index, positions, out):
+    """out[t] = x[t] + (x[t - 1] - x[t]) * mu in float32, x float32 [T, W]; the row before a portion's first token is
+    state[slot, state_off : state_off + W] (zeros in a fresh slot), which the launch replaces by the portion's last row."""
+    _need(x, torch.float32, "x", 2); _need(mu, torch.float32, "mu", 1); _need(out, None, "out", 2)
+    T, W = x.shape
+    if mu.shape[0] != W or out.shape != (T, W) or req_index.shape[0] != T or positions.shape[0] != T:
+        raise KernelError("token_shift: shapes disagree")
+    base, stride = _state_args(state, state_off, W)
+    B = _seg_args(cu, slots)
+    _need(req_index, torch.int32, "req_index", 1); _need(positions, torch.int32, "positions", 1)
+    _check(_fn("recurrent", "vl_token_shift")(_ptr(x), _ptr(mu), base, stride, _ptr(cu), _ptr(slots), _ptr(req_index),
+                                              _ptr(positions), _ptr(out), dtype_code(out.dtype), T, W, _stream()),
+           "vl_token_shift")
+    return out
+
+
 # ---------------------------------------------------------------- attention
 def _check_sinks(sinks, num_heads):
     if sinks is not None:
@@ -270,11 +329,41 @@ def _check_sinks(sinks, num_heads):
             raise KernelError(f"sinks must hold one number per query head ({num_heads}), got {sinks.shape[0]}")
 
 
+WEIGHTINGS = {"softmax": 0, "sigmoid": 1}
+
+
+def _check_variant(qkv, num_heads, weighting, chunk, head_bias, gate, sinks):
+    """The options every attention entry point shares: `weighting` "softmax", or "sigmoid" (a visible key weighs
+    sigmoid(score + head_bias[h]) by itself, nothing is divided by a sum; no sinks); `chunk`: positions in blocks of
+    that many, a query reads no key of an earlier block; `gate` [T, >= nq] in the activation dtype (a view whose rows
+    may be wider): head h's output for token t is multiplied by sigmoid(gate[t, h]).  Returns (mode, chunk, gate stride)."""
+    if weighting not in WEIGHTINGS:
+        raise KernelError(f"attention weighting {weighting!r}; known: {', '.join(WEIGHTINGS)}")
+    if weighting == "sigmoid" and sinks is not None:
+        raise KernelError("a sink belongs to a softmax")
+    if head_bias is not None:
+        _need(head_bias, torch.float32, "head_bias", 1)
+        if weighting != "sigmoid" or head_bias.shape[0] != num_heads:
+            raise KernelError("head_bias: one float32 number per query head, for the sigmoid weighting")
+    stride = 0
+    if gate is not None:
+        if not gate.is_cuda or gate.dtype != qkv.dtype or gate.dim() != 2 or gate.shape[0] != qkv.shape[0] \
+                or gate.shape[1] < num_heads or gate.stride(1) != 1:
+            raise KernelError("gate must be [T, >= heads] in the activation dtype with unit stride along the heads")
+        stride = gate.stride(0)
+    if chunk is not None and chunk <= 0:
+        raise KernelError(f"a chunk of {chunk} positions")
+    return WEIGHTINGS[weighting], int(chunk or 0), stride
+
+
 def paged_attention(qkv, out, k_cache, v_cache, block_table, req_index, positions,
-                    num_heads, num_kv_heads, head_dim, scale, window, err, sinks=None):
+                    num_heads, num_kv_heads, head_dim, scale, window, err, sinks=None,
+                    weighting="softmax", chunk=None, head_bias=None, gate=None):
     """out [T, nq*hd] = attention of the q part of qkv over the pages of each token's request.
-    `sinks` (float32 [nq]): one more term exp(sinks[h]) in every softmax denominator of head h."""
+    `sinks` (float32 [nq]): one more term exp(sinks[h]) in every softmax denominator of head h.
+    `weighting`, `chunk`, `head_bias`, `gate`: see `_check_variant`."""
     _check_sinks(sinks, num_heads)
+    mode, chunk, gate_stride = _check_variant(qkv, num_heads, weighting, chunk, head_bias, gate, sinks)
     _need(qkv, None, "qkv", 2); _need(out, qkv.dtype, "out", 2)
     _need(k_cache, qkv.dtype, "k_cache", 4); _need(v_cache, qkv.dtype, "v_cache", 4)
     _need(block_table, torch.int32, "block_table", 2)
@@ -290,7 +379,8 @@ def paged_attention(qkv, out, k_cache, v_cache, block_table, req_index, position
         _ptr(qkv), qkv.shape[1], _ptr(out), dtype_code(qkv.dtype), _ptr(k_cache), _ptr(v_cache),
         _ptr(block_table), block_table.shape[1], _ptr(req_index), _ptr(positions),
         T, num_heads, num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0],
-        float(scale), int(window or 0), _ptr(sinks), _ptr(err), _stream()), "vl_paged_attention")
+        float(scale), int(window or 0), _ptr(sinks), mode, chunk, _ptr(head_bias), _ptr(gate), gate_stride,
+        _ptr(err), _stream()), "vl_paged_attention")
     return out
 
 
@@ -552,6 +642,25 @@ def silu_mul(gate_up, out, group=0):
 
 
 ACTIVATIONS = {"silu": 0, "relu": 1, "capped_swish": 2}
+# functions of ONE argument (an expert without a gate: down(f(up h))); the codes continue the gated ones
+UNARY_ACTIVATIONS = {"relu2": 16}           # the square of max(v, 0)
+
+
+def _act_code(act) -> int:
+    """The kernels' code of an activation name (None: -1); codes from 16 on are functions of one argument."""
+    if act is None:
+        return -1
+    return ACTIVATIONS[act] if act in ACTIVATIONS else UNARY_ACTIVATIONS[act]
+
+
+def unary_act(x, out, act):
+    """out = f(x) element by element (float32 inside); f from UNARY_ACTIVATIONS."""
+    _need(x, None, "x"); _need(out, x.dtype, "out")
+    if x.numel() != out.numel():
+        raise KernelError("unary_act: sizes differ")
+    _check(_fn("activation", "vl_unary_act")(_ptr(x), _ptr(out), dtype_code(x.dtype), x.numel(), UNARY_ACTIVATIONS[act],
+                                             _stream()), "vl_unary_act")
+    return out
 
 
 def gated_act(gate_up, out, act, group=0, alpha=1.0, limit=0.0, shift=0.0, bias=None):
@@ -605,6 +714,21 @@ def layernorm_add(y, weight, eps, x, cast=None):
             raise KernelError("layernorm_add: cast must have the stream's shape")
     _check(_fn("embed_norm", "vl_layernorm_add")(_ptr(y), dtype_code(y.dtype), _ptr(weight), float(eps), _ptr(x), _ptr(cast),
                                                  x.shape[0], x.shape[1], _stream()), "vl_layernorm_add")
+    return x
+
+
+def rmsnorm_add(y, weight, eps, mult, x, cast=None):
+    """x[r] += mult * (y[r] / sqrt(mean(y[r]^2) + eps) * weight), x float32 [R, H], y in the activation dtype; `cast`
+    (same dtype as y, or None) receives the new x."""
+    _need(y, None, "y", 2); _need(x, torch.float32, "x", 2); _need(weight, torch.float32, "weight", 1)
+    if y.shape != x.shape or weight.shape[0] != x.shape[1]:
+        raise KernelError(f"rmsnorm_add: y {tuple(y.shape)}, x {tuple(x.shape)}, weight {tuple(weight.shape)}")
+    if cast is not None:
+        _need(cast, y.dtype, "cast", 2)
+        if cast.shape != x.shape:
+            raise KernelError("rmsnorm_add: cast must have the shape of x")
+    _check(_fn("embed_norm", "vl_rmsnorm_add")(_ptr(y), dtype_code(y.dtype), _ptr(weight), float(eps), float(mult), _ptr(x),
+                                               _ptr(cast), x.shape[0], x.shape[1], _stream()), "vl_rmsnorm_add")
     return x
 
 
@@ -681,7 +805,7 @@ def gemm_grouped_fused_ok(dtype, K, N, act=None) -> bool:
         return False
     fn = build.load("gemm_batched").vl_gemm_grouped_fused_ok
     fn.argtypes, fn.restype = [c_int, c_int, c_int], c_int
-    return bool(fn(int(K), int(N), -1 if act is None else ACTIVATIONS[act]))
+    return bool(fn(int(K), int(N), _act_code(act)))
 
 
 def gemm_grouped_fused(a, w, out, tile_group, bm, row_index, index_div, row_scale=None, act=None, alpha=1.0, limit=0.0,
@@ -689,19 +813,20 @@ def gemm_grouped_fused(a, w, out, tile_group, bm, row_index, index_div, row_scal
     """The grouped product with a routed feed-forward's neighbours folded in (bfloat16, tensor cores):
     sorted row m is row row_index[m] // index_div of a [rows, K] (negative: zeros), times w[tile_group[y]]
     ([G, N, K]); the float32 sums are multiplied by row_scale[row_index[m]] when given; with `act`, w holds
-    blocks of 8 gate rows and their 8 up rows and out is [cap, N / 2] = act(gate, up), else out is [cap, N]."""
+    blocks of 8 gate rows and their 8 up rows and out is [cap, N / 2] = act(gate, up), else out is [cap, N]; an `act`
+    of UNARY_ACTIVATIONS is applied to every column of a plain w (out [cap, N])."""
     _need(a, torch.bfloat16, "a", 2); _need(w, torch.bfloat16, "w", 3); _need(out, torch.bfloat16, "out", 2)
     _need(tile_group, torch.int32, "tile_group", 1); _need(row_index, torch.int32, "row_index", 1)
     G, N, K = w.shape
     cap = row_index.shape[0]
-    width = N // 2 if act is not None else N
+    width = N // 2 if act in ACTIVATIONS else N
     if a.shape[1] != K or out.shape != (cap, width) or cap % bm or tile_group.shape[0] < cap // bm:
         raise KernelError("gemm_grouped_fused: shapes disagree")
     if row_scale is not None:
         _need(row_scale, torch.float32, "row_scale")
     _check(_fn("gemm_batched", "vl_gemm_grouped_fused")(
         _ptr(a), _ptr(w), _ptr(out), cap, N, K, K, width, _ptr(tile_group), N * K, int(bm), _ptr(row_index), int(index_div),
-        _ptr(row_scale), -1 if act is None else ACTIVATIONS[act], float(alpha), float(limit), float(shift), _stream()),
+        _ptr(row_scale), _act_code(act), float(alpha), float(limit), float(shift), _stream()),
         "vl_gemm_grouped_fused")
     return out
 
@@ -725,13 +850,15 @@ def router_slices(K) -> int:
     return 1
 
 
-def moe_route(h, router, top, ids, weights, logits, score="sigmoid", renormalize=False, groups=1, keep_groups=1):
+def moe_route(h, router, top, ids, weights, logits, score="sigmoid", renormalize=False, groups=1, keep_groups=1, bias=None):
     """h [T, K], router [E, K] (float32; or bfloat16 as stored, beside bfloat16 rows: products of two bfloat16 numbers
     are exact in float32, so the tensor cores' float32 sums are the 32-bit logits of the rounded rows):
     logits float32 [router_slices(K), T, E] = partial sums of h router^T; ids int32 [T, top] = the experts with
     the largest logits, weights float32 [T, top] = their scores (divided by their sum when `renormalize`).
     `groups` > 1: the experts form that many equal groups of neighbours, a group counts by its largest logit, and only
-    experts of the `keep_groups` best groups are chosen from (scores are still taken over all experts)."""
+    experts of the `keep_groups` best groups are chosen from (scores are still taken over all experts).
+    `bias` (float32 [E]) is added to the logits before anything else.  "softmax" with `renormalize` is the softmax
+    over the chosen logits alone."""
     _need(h, None, "h", 2); _need(router, None, "router", 2); _need(logits, torch.float32, "logits", 3)
     if router.dtype != torch.float32 and router.dtype != h.dtype:
         raise KernelError("moe_route: the router is float32, or bfloat16 beside bfloat16 rows")
@@ -745,8 +872,13 @@ def moe_route(h, router, top, ids, weights, logits, score="sigmoid", renormalize
                                                     _ptr(logits), T, E, K, slices, _stream()), "vl_gemm_rows_f32w")
     if groups < 1 or E % groups or not 1 <= keep_groups <= groups or keep_groups * (E // groups) < top:
         raise KernelError(f"moe_route: {E} experts in {groups} groups, {keep_groups} kept, top {top}")
+    if bias is not None:
+        _need(bias, torch.float32, "bias", 1)
+        if bias.shape[0] != E:
+            raise KernelError(f"moe_route: the router's bias has {bias.shape[0]} entries for {E} experts")
     _check(_fn("moe", "vl_moe_route")(_ptr(logits), slices, T, E, int(top), ROUTER_SCORES[score], int(bool(renormalize)),
-                                      int(groups), int(keep_groups), _ptr(ids), _ptr(weights), _stream()), "vl_moe_route")
+                                      int(groups), int(keep_groups), _ptr(bias), _ptr(ids), _ptr(weights), _stream()),
+           "vl_moe_route")
 
 
 TC5_GROUPED_TILE = 128    # rows per tile of the grouped tcgen05 product
@@ -766,12 +898,12 @@ def gemm_grouped_tc5(rows, w, out, tile_group, err, row_index=None, row_scale=No
     _need(tile_group, torch.int32, "tile_group", 1)
     G, N, K = w.shape
     cap = rows.shape[0]
-    if rows.shape[1] != K or out.shape != (cap, N // 2 if act is not None else N) or cap % TC5_GROUPED_TILE \
+    if rows.shape[1] != K or out.shape != (cap, N // 2 if act in ACTIVATIONS else N) or cap % TC5_GROUPED_TILE \
             or tile_group.shape[0] < cap // TC5_GROUPED_TILE:
         raise KernelError("gemm_grouped_tc5: shapes disagree")
     _check(_fn("gemm_tc5_grouped", "vl_gemm_bf16_tc5_grouped")(
         _ptr(rows), _ptr(w), _ptr(out), cap, N, K, G, _ptr(tile_group), _ptr(row_index), _ptr(row_scale),
-        -1 if act is None else ACTIVATIONS[act], float(alpha), float(limit), float(shift), _ptr(err), _stream()),
+        _act_code(act), float(alpha), float(limit), float(shift), _ptr(err), _stream()),
         "vl_gemm_bf16_tc5_grouped")
     return out
 

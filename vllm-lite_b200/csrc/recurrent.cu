@@ -9,6 +9,7 @@
 //   vl_short_conv   out[t, c] = act(bias[c] + sum_j w[c, j] in[t - (taps-1) + j, c]), zeros before a request's
 //                   first token; the last taps-1 inputs of every channel are part of the state (`longest`: a bound
 //                   on the tokens a request brings, which says how many blocks share a request)
+//   vl_token_shift  h[t] = x[t] + (x[t-1] - x[t]) mu, the row before a portion's first token being part of the state
 //   vl_ssd_scan     S <- exp(-exp(A_log) dt) S + dt B x^T,  y = S^T C + D x          (S: N x P per head, dt =
 //                   softplus(raw + bias); heads share B and C in groups)
 //   vl_mlstm_scan   m' = max(f + m, i);  S <- e^(f+m-m') S + e^(i-m') k v^T;  n likewise with k alone;
@@ -133,6 +134,58 @@ extern "C" int vl_short_conv(const void* in, int dtype, int ld, int col0, int C,
         if (rc) return rc;
     }
     return VL_OK;
+}
+
+// ------------------------------------------------------------------------------------------ token shift
+// h[t] = x[t] + (x[t - 1] - x[t]) * mu, element by element in float32, with x[t - 1] the row of the request's token
+// before (the state's row for the first token of a portion; a fresh slot holds zeros).  The block of a portion's
+// first token also leaves the portion's LAST row of x in the state: a thread reads the old value of its elements
+// before it writes the new one, and no other block touches that state, so one launch serves portions of any length.
+// A row at a negative position (a padded row of a replayed step) passes unchanged and touches no state.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+token_shift_kernel(const float* __restrict__ x, const float* __restrict__ mu, float* __restrict__ state,
+                   long long state_stride, const int* __restrict__ cu, const int* __restrict__ slots,
+                   const int* __restrict__ req_index, const int* __restrict__ positions, TO* __restrict__ out, int W) {
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int b = req_index[t], pos = positions[t];
+    const bool live = pos >= 0;
+    const int first = live ? cu[b] : 0, last = live ? cu[b + 1] - 1 : 0;
+    pdl_wait();
+    const float* xr = x + (size_t)t * W;
+    TO* o = out + (size_t)t * W;
+    if (!live) {
+        for (int i = threadIdx.x; i < W; i += 256) o[i] = from_f32<TO>(xr[i]);
+        return;
+    }
+    if (t != first) {
+        const float* before = xr - W;
+        for (int i = threadIdx.x; i < W; i += 256) { const float v = xr[i]; o[i] = from_f32<TO>(v + (before[i] - v) * mu[i]); }
+        return;
+    }
+    float* st = state + (long long)slots[b] * state_stride;
+    const float* keep = x + (size_t)last * W;
+    for (int i = threadIdx.x; i < W; i += 256) {
+        const float v = xr[i], before = st[i];
+        st[i] = keep[i];
+        o[i] = from_f32<TO>(v + (before - v) * mu[i]);
+    }
+}
+
+extern "C" int vl_token_shift(const float* x, const float* mu, float* state, long long state_stride, const int* cu,
+                              const int* slots, const int* req_index, const int* positions, void* out, int dtype, int T, int W,
+                              void* stream) {
+    if (T <= 0) return VL_OK;
+    if (W <= 0 || state_stride < W) return VL_ERR_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VL_F32)
+        return vl_launch(token_shift_kernel<float>, dim3(T), dim3(256), 0, s, x, mu, state, state_stride, cu, slots, req_index,
+                         positions, (float*)out, W);
+    if (dtype == VL_BF16)
+        return vl_launch(token_shift_kernel<bf16>, dim3(T), dim3(256), 0, s, x, mu, state, state_stride, cu, slots, req_index,
+                         positions, (bf16*)out, W);
+    return VL_ERR_UNSUPPORTED;
 }
 
 // ------------------------------------------------------------------------------------------ the scans' frame

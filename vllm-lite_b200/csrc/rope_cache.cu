@@ -240,3 +240,103 @@ extern "C" int vl_qk_norm_rope_write(
 #undef ROPE_LAUNCH
     return VL_ERR_UNSUPPORTED;
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// The same step for a mixer that norms q and k over the WHOLE projection and whose values are its keys:
+//   in [T, ld] float32 = q (nq * hd) | k (nkv * hd), e.g. as a short convolution left them;
+//   v <- k as it came;   q <- q / sqrt(mean over all nq * hd values of q^2 + eps) * qw, k likewise with kw
+//   (qw, kw of nq * hd and nkv * hd entries), then the rotation of the first `rot` features of every head
+//   (pairs (i, i + rot/2)), q to q_out [T, nq * hdp], k and v to the token's cache slot (heads of hdp features).
+// hdp >= hd is the head size the attention kernels see; features hd .. hdp - 1 are written as zeros.
+// One block per token; sums of squares, angles, sine and cosine in float32.  A token at a negative position
+// (a padded row of a replayed step) gets zeros for q and writes no cache.
+// ---------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(ROPE_THREADS)
+rows_norm_rope_write_kernel(const float* __restrict__ in, int ld, const int* __restrict__ positions,
+                            const int* __restrict__ slots, const float* __restrict__ qw, const float* __restrict__ kw,
+                            float eps, const float* __restrict__ inv_freq, int rot, T* __restrict__ q_out,
+                            T* __restrict__ kcache, T* __restrict__ vcache, int nq, int nkv, int hd, int hdp, int page_size,
+                            long long num_slots, unsigned* err) {
+    __shared__ float s_cos[ROPE_MAX_HD / 2], s_sin[ROPE_MAX_HD / 2];
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int p = positions[t];
+    const int half = inv_freq ? rot / 2 : 0;
+    const int Cq = nq * hd, Ck = nkv * hd;
+    if (inv_freq) {
+        const float pos = (float)p;
+        for (int i = threadIdx.x; i < half; i += ROPE_THREADS) sincosf(pos * inv_freq[i], &s_sin[i], &s_cos[i]);
+    }
+    pdl_wait();
+    T* qo = q_out + (size_t)t * nq * hdp;
+    if (p < 0) {
+        for (int e = threadIdx.x; e < nq * hdp; e += ROPE_THREADS) qo[e] = from_f32<T>(0.f);
+        return;
+    }
+    const float* row = in + (size_t)t * ld;
+    float ssq = 0.f, ssk = 0.f;
+    for (int e = threadIdx.x; e < Cq; e += ROPE_THREADS) { const float v = row[e]; ssq += v * v; }
+    for (int e = threadIdx.x; e < Ck; e += ROPE_THREADS) { const float v = row[Cq + e]; ssk += v * v; }
+    ssq = block_sum<ROPE_THREADS>(ssq, scratch);
+    ssk = block_sum<ROPE_THREADS>(ssk, scratch);          // (block_sum's own barriers order the table above, too)
+    const float invq = 1.0f / sqrtf(ssq / (float)Cq + eps), invk = 1.0f / sqrtf(ssk / (float)Ck + eps);
+    for (int o = threadIdx.x; o < nq * hdp; o += ROPE_THREADS) {
+        const int h = o / hdp, d = o - h * hdp, e = h * hd + d;
+        float v = 0.f;
+        if (d < hd) {
+            v = row[e] * invq * qw[e];
+            if (d < 2 * half) {
+                const bool first = d < half;
+                const int pe = first ? e + half : e - half, i = first ? d : d - half;
+                const float other = row[pe] * invq * qw[pe];
+                v = first ? v * s_cos[i] - other * s_sin[i] : v * s_cos[i] + other * s_sin[i];
+            }
+        }
+        qo[o] = from_f32<T>(v);
+    }
+    if (!slots) return;
+    const int slot = slots[t];
+    if (slot < 0) return;
+    if (slot >= num_slots) {
+        if (threadIdx.x == 0) atomicOr(err, VL_DEV_BAD_SLOT);
+        return;
+    }
+    const int page = slot / page_size, off = slot - page * page_size;
+    const float* krow = row + Cq;
+    for (int o = threadIdx.x; o < nkv * hdp; o += ROPE_THREADS) {
+        const int kvh = o / hdp, d = o - kvh * hdp, e = kvh * hd + d;
+        float v = 0.f, raw = 0.f;
+        if (d < hd) {
+            raw = krow[e];
+            v = raw * invk * kw[e];
+            if (d < 2 * half) {
+                const bool first = d < half;
+                const int pe = first ? e + half : e - half, i = first ? d : d - half;
+                const float other = krow[pe] * invk * kw[pe];
+                v = first ? v * s_cos[i] - other * s_sin[i] : v * s_cos[i] + other * s_sin[i];
+            }
+        }
+        const size_t at = (((size_t)page * nkv + kvh) * page_size + off) * hdp + d;
+        kcache[at] = from_f32<T>(v);
+        vcache[at] = from_f32<T>(raw);
+    }
+}
+
+extern "C" int vl_rows_norm_rope_write(const float* in, int ld, const int* positions, const int* slots, const float* qw,
+                                       const float* kw, float eps, const float* inv_freq, int rot, void* q_out, int dtype,
+                                       void* kcache, void* vcache, int T, int nq, int nkv, int hd, int hdp, int page_size,
+                                       long long num_slots, unsigned* err, void* stream) {
+    if (T <= 0) return VL_OK;
+    if (hd <= 0 || hdp < hd || nq <= 0 || nkv <= 0 || rot < 0 || rot > hd || (rot & 1) || rot > ROPE_MAX_HD) return VL_ERR_UNSUPPORTED;
+    if (page_size <= 0 || ld < (nq + nkv) * hd || !qw || !kw) return VL_ERR_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VL_F32)
+        return vl_launch(rows_norm_rope_write_kernel<float>, dim3(T), dim3(ROPE_THREADS), 0, s, in, ld, positions, slots, qw, kw,
+                         eps, inv_freq, rot, (float*)q_out, (float*)kcache, (float*)vcache, nq, nkv, hd, hdp, page_size, num_slots, err);
+    if (dtype == VL_BF16)
+        return vl_launch(rows_norm_rope_write_kernel<bf16>, dim3(T), dim3(ROPE_THREADS), 0, s, in, ld, positions, slots, qw, kw,
+                         eps, inv_freq, rot, (bf16*)q_out, (bf16*)kcache, (bf16*)vcache, nq, nkv, hd, hdp, page_size, num_slots, err);
+    return VL_ERR_UNSUPPORTED;
+}

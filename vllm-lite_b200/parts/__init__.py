@@ -5,4 +5,4 @@ from . import norm, rope, attention, mlp, block, embedding, head   # noqa: F401 
 from . import latent_attention, gated_mlp, experts               # noqa: F401  (registration)
 from .model import CausalLM, cache_needs, declare_model  # noqa: F401
 from .registry import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS  # noqa: F401
-from . import recurrent, parallel                                 # noqa: F401  (registration)
+from . import recurrent, parallel, conv_attention, token_shift    # noqa: F401  (registration)

@@ -57,12 +57,18 @@ def _decode(ops, args, step, spec, group, num_tokens, max_context, token_index=N
                             arrivals=arrivals, fold=fold, sinks=sinks)
 
 
-def run(qkv, out, cache, group, step, spec, scale, fold=None, sinks=None):
+def run(qkv, out, cache, group, step, spec, scale, fold=None, sinks=None, weighting="softmax", chunk=None,
+        head_bias=None, gate=None):
     """`spec`: anything with num_heads, num_kv_heads, head_dim and window.
     `fold` (only where `folds_head_work` said so): (q_weight, k_weight, eps, inv_freq, rotary_dim, slots) of the
     head work that the mixer left undone.
-    `sinks` (float32 [num_heads]): a number per head that joins every softmax denominator as exp(sink)."""
+    `sinks` (float32 [num_heads]): a number per head that joins every softmax denominator as exp(sink).
+    `weighting` "sigmoid" (with `head_bias`, float32 [num_heads]): a key weighs sigmoid(score + head_bias[h]) by
+    itself; `chunk`: positions in blocks of that many, no key of an earlier block is read; `gate` [T, >= num_heads]:
+    head h's output is multiplied by sigmoid(gate[t, h])."""
     from ..csrc import ops
+    if weighting != "softmax" or chunk is not None or head_bias is not None or gate is not None:
+        return _run_variant(ops, qkv, out, cache, group, step, spec, scale, weighting, chunk, head_bias, gate, sinks)
     if fold is not None and not folds_head_work(qkv.dtype, step, spec, group, qkv.shape[0]):
         raise ValueError("this step's attention kernel does not fold the head norm and rotation in")
     args = (qkv, out, cache.k, cache.v, group.block_table, step.req_index, step.positions,
@@ -82,3 +88,10 @@ def run(qkv, out, cache, group, step, spec, scale, fold=None, sinks=None):
                         token_index=step.single_tokens, sinks=sinks)
             return out
     return ops.paged_attention(*args, step.err, sinks=sinks)
+
+
+def _run_variant(ops, q, out, cache, group, step, spec, scale, weighting, chunk, head_bias, gate, sinks):
+    """Attention with another weighting than the softmax, a chunked mask or an output gate."""
+    return ops.paged_attention(q, out, cache.k, cache.v, group.block_table, step.req_index, step.positions,
+                               spec.num_heads, spec.num_kv_heads, spec.head_dim, scale, spec.window, step.err, sinks=sinks,
+                               weighting=weighting, chunk=chunk, head_bias=head_bias, gate=gate)

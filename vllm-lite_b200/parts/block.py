@@ -80,8 +80,9 @@ def _sink(residual, norm) -> StreamSink:
 
 @BLOCKS.register("post_norm")
 class PostNormBlock:
-    """x += norm1(mixer(x)); x += norm2(ffn(x)): the norms sit on the sub-layers' outputs and the sub-layers
-    read the stream itself (its rounding to the activation dtype).  The norm's kernel adds its result into
+    """x += m norm1(mixer(x)); x += m norm2(ffn(x)) (m = `spec.residual_mult`): the norms sit on the sub-layers' outputs
+    and the sub-layers read the stream itself (its rounding to the activation dtype; a mixer that says `reads_stream`
+    is given the float32 stream as it is).  The norm's kernel adds its result into
     the float32 stream and leaves the new stream in the activation dtype for the next sub-layer.  A block
     without a feed-forward (`spec.ffn` None) is its first half alone."""
 
@@ -114,6 +115,7 @@ class PostNormBlock:
             if norm is not None and not hasattr(norm, "add_normed"):
                 raise TypeError(f"norm kind {norm.spec.kind!r} cannot norm a sub-layer's output into the stream: "
                                 f"it offers no add_normed(y, x, step, cast)")
+        self.mult = float(spec.residual_mult)
         self.graph_safe = bool(getattr(self.mixer, "graph_safe", False)
                                and (self.ffn is None or getattr(self.ffn, "graph_safe", False)))
 
@@ -129,13 +131,23 @@ class PostNormBlock:
         return residual.cast, buf
 
     def __call__(self, residual, step, cache):
-        h, buf = self._stream_input(residual, step)
-        y = self.mixer(h, step, cache)
-        residual.cast = self.norm1.add_normed(y, residual.x, step, buf)
+        kw = {} if self.mult == 1.0 else {"mult": self.mult}
+        if getattr(self.mixer, "reads_stream", False):
+            # the mixer's first step works on the float32 stream itself (and on other rows of it)
+            if residual.pending is not None or residual.normed is not None:
+                raise NotImplementedError("a post-norm block after a block that leaves its result pending")
+            buf = None if self.dtype == torch.float32 else step.workspace.get(step.tag + "stream.cast", residual.x.shape, self.dtype)
+            y = self.mixer(residual.x, step, cache)
+        else:
+            h, buf = self._stream_input(residual, step)
+            y = self.mixer(h, step, cache)
+        # the feed-forward reads the new stream in the activation dtype; after the last norm of the block only a
+        # following block that asks for it does
+        residual.cast = self.norm1.add_normed(y, residual.x, step, buf, **kw)
         if self.ffn is not None:
             h = residual.x if buf is None else residual.cast
             y = self.ffn(h, step)
-            residual.cast = self.norm2.add_normed(y, residual.x, step, buf)
+            residual.cast = self.norm2.add_normed(y, residual.x, step, buf, **kw)
 
 
 def _exact(weights, prefix, norm_spec):

@@ -1,4 +1,4 @@
-"""Token embedding: x[t] = table[id[t]], a row gather into the float32 residual stream, no scaling
+"""Token embedding: x[t] = table[id[t]] * scale, a row gather into the float32 residual stream; the reference has no scaling
 (crates/model/src/causal_lm/mod.rs:28-46 of the reference).
 
 An embedding part offers
@@ -30,4 +30,4 @@ class TokenEmbedding:
 
     def __call__(self, step, x):
         from ..csrc import ops
-        return ops.embed(step.tokens, self.table, x, step.err)     # an id outside the table is flagged, not read
+        return ops.embed(step.tokens, self.table, x, step.err, self.spec.scale)     # an id outside the table is flagged, not read

@@ -5,6 +5,7 @@
        or sum_e w_e E_e(h)
     E(y) = W_down (f(W_gate y, W_up y)),  f as in `ops.gated_act` (for "capped_swish":
            g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(alpha g') (u' + up_shift))
+       or, for an expert without a gate (`gated` False), W_down f(W_up y) with f of `ops.UNARY_ACTIVATIONS`
 
 No host decision anywhere, so a step stays a fixed sequence of launches (and a decode step a CUDA graph):
 the router kernel writes ids and weights, one block sorts the (token, choice) pairs by expert into tiles
@@ -37,9 +38,13 @@ class RoutedExperts:
         gate, up, down = spec.names
         I, H = spec.intermediate_size, spec.hidden_size
         d = {spec.router: TensorDecl((spec.num_experts, H))}
+        if spec.router_bias is not None:
+            d[spec.router + spec.router_bias] = TensorDecl((spec.num_experts,))
         for e in range(spec.num_experts):
             p = spec.expert_prefix.format(e)
-            d.update({p + gate: TensorDecl((I, H)), p + up: TensorDecl((I, H)), p + down: TensorDecl((H, I))})
+            d.update({p + up: TensorDecl((I, H)), p + down: TensorDecl((H, I))})
+            if spec.gated:
+                d[p + gate] = TensorDecl((I, H))
         return d
 
     def __init__(self, spec: RoutedExpertsSpec, weights: dict, ctx):
@@ -50,8 +55,10 @@ class RoutedExperts:
                 or spec.keep_groups * (spec.num_experts // spec.groups) < spec.top:
             raise ValueError(f"routed experts: {spec.num_experts} experts in {spec.groups} groups of which {spec.keep_groups} "
                              f"are kept cannot offer {spec.top} choices")
-        if spec.activation not in ops.ACTIVATIONS or spec.score not in ops.ROUTER_SCORES:
-            raise ValueError(f"routed experts: activation {spec.activation!r} / score {spec.score!r} not known")
+        known = ops.ACTIVATIONS if spec.gated else ops.UNARY_ACTIVATIONS
+        if spec.activation not in known or spec.score not in ops.ROUTER_SCORES:
+            raise ValueError(f"routed experts: activation {spec.activation!r} ({'with' if spec.gated else 'without'} a gate) / "
+                             f"score {spec.score!r} not known")
         self.spec = spec
         self.dtype = ctx.dtype
         gate, up, down = spec.names
@@ -63,9 +70,16 @@ class RoutedExperts:
         r = weights[spec.router]
         keep = r.dtype == torch.bfloat16 and ctx.dtype == torch.bfloat16 and spec.hidden_size % 8 == 0
         self.router = r.contiguous() if keep else r.to(device=ctx.device, dtype=torch.float32).contiguous()
+        self.router_bias = None
+        if spec.router_bias is not None:
+            self.router_bias = weights[spec.router + spec.router_bias].to(device=ctx.device, dtype=torch.float32).contiguous()
         I, H = spec.intermediate_size, spec.hidden_size
-        self.fused = I % 8 == 0 and ops.gemm_grouped_fused_ok(ctx.dtype, H, 2 * I, spec.activation)
-        if self.fused:
+        # columns of the first product: gate and up rows, or the up rows alone
+        self.first_n = 2 * I if spec.gated else I
+        self.fused = I % 8 == 0 and ops.gemm_grouped_fused_ok(ctx.dtype, H, self.first_n, spec.activation)
+        if not spec.gated:
+            self.gate_up = torch.stack([weights[p + up] for p in names]).contiguous()           # [E, I, H]
+        elif self.fused:
             # per expert blocks of 8 gate rows followed by their 8 up rows: [E, 2I, H]
             self.gate_up = torch.stack([torch.stack([weights[p + gate].view(I // 8, 8, H), weights[p + up].view(I // 8, 8, H)],
                                                     dim=1).reshape(2 * I, H) for p in names]).contiguous()
@@ -90,7 +104,8 @@ class RoutedExperts:
         tile_group = ws.get(tag + "moe.tiles", (cap // bm,), torch.int32)
         place = ws.get(tag + "moe.place", (pairs,), torch.int32)
         logits = ws.get(tag + "moe.logits", (ops.router_slices(H), T, E), torch.float32)
-        ops.moe_route(h, self.router, top, ids, weights, logits, s.score, s.renormalize, s.groups, s.keep_groups)
+        ops.moe_route(h, self.router, top, ids, weights, logits, s.score, s.renormalize, s.groups, s.keep_groups,
+                      bias=self.router_bias)
         ops.moe_align(ids, E, bm, sorted_rows, tile_group, place)
         act = ws.get(tag + "moe.act", (cap, I), self.dtype)
         if big:
@@ -105,8 +120,11 @@ class RoutedExperts:
                                    weights if s.scale_input else None, s.activation, s.alpha, s.limit, s.up_shift)
         else:
             rows = ops.moe_gather(h, sorted_rows, weights, top, ws.get(tag + "moe.rows", (cap, H), self.dtype), s.scale_input)
-            gu = ops.gemm_grouped(rows, self.gate_up, ws.get(tag + "moe.gate_up", (cap, 2 * I), self.dtype), tile_group, bm)
-            ops.gated_act(gu, act, s.activation, 0, s.alpha, s.limit, s.up_shift)
+            gu = ops.gemm_grouped(rows, self.gate_up, ws.get(tag + "moe.gate_up", (cap, self.first_n), self.dtype), tile_group, bm)
+            if s.gated:
+                ops.gated_act(gu, act, s.activation, 0, s.alpha, s.limit, s.up_shift)
+            else:
+                ops.unary_act(gu, act, s.activation)
         res = ops.gemm_grouped(act, self.down, ws.get(tag + "moe.down", (cap, H), self.dtype), tile_group, bm)
         out = ws.get(tag + "moe.out", (T, H), self.dtype)
         return ops.moe_combine(res, place, weights, top, out, not s.scale_input)

@@ -21,7 +21,7 @@ class LinearHead:
 
     @staticmethod
     def declare(spec: HeadSpec) -> dict:
-        return {} if spec.tied else {"weight": TensorDecl((spec.vocab_size, spec.hidden_size))}
+        return {} if spec.tied else {spec.tensor: TensorDecl((spec.vocab_size, spec.hidden_size))}
 
     def __init__(self, spec: HeadSpec, weights: dict, ctx, embedding=None):
         self.spec = spec
@@ -30,7 +30,7 @@ class LinearHead:
             if weight is None or tuple(weight.shape) != (spec.vocab_size, spec.hidden_size):
                 raise ValueError("a tied output head needs an embedding that shares a [vocab, hidden] table")
         else:
-            weight = weights["weight"]
+            weight = weights[spec.tensor]
         self.proj = Linear(weight)
 
     def __call__(self, h, step):

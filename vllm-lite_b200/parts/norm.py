@@ -15,13 +15,22 @@ class RmsNorm:
 
     @staticmethod
     def declare(spec: NormSpec) -> dict:
-        return {spec.tensor: TensorDecl((spec.size,), init="norm")}
+        return {spec.tensor: TensorDecl(() if spec.scalar else (spec.size,), init="norm")}
 
     def __init__(self, spec: NormSpec, weights: dict, ctx):
         self.spec = spec
         self.dtype = ctx.dtype
-        # A vector of `size` numbers: kept as float32 on the device (exact from bfloat16).
-        self.weight = weights[spec.tensor].to(device=ctx.device, dtype=torch.float32).contiguous()
+        # A vector of `size` numbers: kept as float32 on the device (exact from bfloat16).  A norm with one number
+        # for all coordinates holds that number `size` times, so every kernel sees a vector.
+        w = weights[spec.tensor].to(device=ctx.device, dtype=torch.float32)
+        self.weight = (w.reshape(1).expand(spec.size) if spec.scalar else w).contiguous()
+
+    def add_normed(self, y, x, step, cast=None, mult=1.0):
+        """x += mult * norm(y): what a block that norms its sub-layers' OUTPUTS calls; `cast` (a buffer in the
+        activation dtype, or None) receives the new x.  Returns cast."""
+        from ..csrc import ops
+        ops.rmsnorm_add(y, self.weight, self.spec.eps, mult, x, cast)
+        return cast
 
     def fused_rms(self):
         """(weight, eps): what a kernel that applies this norm itself needs (the attention mixer's
@@ -50,9 +59,11 @@ class LayerNorm:
         self.dtype = ctx.dtype
         self.weight = weights[spec.tensor].to(device=ctx.device, dtype=torch.float32).contiguous()
 
-    def add_normed(self, y, x, step, cast=None):
+    def add_normed(self, y, x, step, cast=None, mult=1.0):
         """x += norm(y); `cast` (a buffer in the activation dtype, or None) receives the new x.  Returns cast."""
         from ..csrc import ops
+        if mult != 1.0:
+            raise NotImplementedError("the layer norm's kernel adds its result as it is")
         ops.layernorm_add(y, self.weight, self.spec.eps, x, cast)
         return cast
 

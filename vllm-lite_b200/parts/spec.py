@@ -37,13 +37,15 @@ class NormSpec:
     """`kind`: "rms_norm" (x / sqrt(mean x^2 + eps) * w), "layer_norm" ((x - mean) / sqrt(var + eps) * w,
     no bias) or "dyn_tanh" (tanh(alpha x) * w + b, alpha a learned scalar: no mean, no variance, eps unused).
     `tensor`: the weight's name relative to the norm's prefix ("" when the prefix is the whole name); a norm with
-    a bias vector or a scalar stores them as `tensor + bias_suffix` / `tensor + alpha_suffix`."""
+    a bias vector or a scalar stores them as `tensor + bias_suffix` / `tensor + alpha_suffix`.
+    `scalar`: the weight is ONE stored number for all `size` coordinates (an "rms_norm" only)."""
     size: int
     eps: float
     kind: str = "rms_norm"
     tensor: str = "weight"
     bias_suffix: str = ".b"
     alpha_suffix: str = ".alpha"
+    scalar: bool = False
 
 
 @dataclass(frozen=True)
@@ -92,11 +94,12 @@ class AttentionSpec:
 
 @dataclass(frozen=True)
 class EmbeddingSpec:
-    """Token ids to rows of the residual stream: x[t] = table[id[t]], no scaling."""
+    """Token ids to rows of the residual stream: x[t] = table[id[t]] * scale (float32)."""
     vocab_size: int
     hidden_size: int
     kind: str = "token_embedding"
     tensor: str = "weight"          # the table's name relative to the embedding's prefix
+    scale: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -107,6 +110,7 @@ class HeadSpec:
     hidden_size: int
     tied: bool = False
     kind: str = "linear_head"
+    tensor: str = "weight"          # the matrix's name relative to the head's prefix (untied)
 
 
 @dataclass(frozen=True)
@@ -170,6 +174,9 @@ class RoutedExpertsSpec:
     `scale_input`: the weight multiplies the expert's input (out = sum_e E_e(w_e h)), else its output.
     Expert: g = gate y, u = up y, no biases; activation "capped_swish": g' = min(g, limit),
     u' = clamp(u, -limit, limit), down(g' sigmoid(alpha g') (u' + up_shift)); "silu" / "relu": down(act(g) u).
+    `gated` False: an expert is down(f(up y)) with f a function of one argument ("relu2": the square of max(v, 0)),
+    and has no gate matrix.  `router_bias`: a vector `router + router_bias` added to the logits.  Score "softmax"
+    with `renormalize` is the softmax over the chosen logits alone.
     Tensors: `router`, and per expert i `expert_prefix.format(i)` + gate / up / down of `names`."""
     hidden_size: int
     intermediate_size: int
@@ -190,6 +197,8 @@ class RoutedExpertsSpec:
     expert_prefix: str = "e{}."
     names: Tuple[str, str, str] = ("gate", "up", "down")
     kind: str = "routed_experts"
+    gated: bool = True
+    router_bias: Optional[str] = None
 
 
 @dataclass(frozen=True)
@@ -256,6 +265,55 @@ class DeltaRuleSpec:
 
 
 @dataclass(frozen=True)
+class ConvAttentionSpec:
+    """Attention whose queries and keys pass a short convolution over time and whose values are its keys.
+
+    q = W_q h (+ b), k = W_k h (+ b) (heads x head_dim, kv_heads x head_dim), each channel through a causal convolution of
+    `conv` taps (no bias, no activation; 1 tap with weight 1 is no convolution); v = k as the convolution leaves it;
+    q and k are then divided by the root mean square of their WHOLE row (all heads at once, eps inside the root) and
+    multiplied by a weight of that size, and `position` turns the first features of every head.
+    score = scale q.k over the keys that `chunk` (positions in blocks of that many from the sequence's start, no key of
+    an earlier block) and `window` (the last that many keys) leave; `weighting` "sigmoid": a key weighs
+    sigmoid(score + pb[head]) by itself (`head_bias`: the tensor pb), nothing is summed to one; "softmax": as usual.
+    `gate`: head h's output is multiplied by sigmoid((W_g h)_h), W_g [heads, hidden].  out = W_o concat (+ b).
+    `names`: (q, k, g, o, pb); a bias is `<name><bias_suffix>`, the taps `<name><conv_suffix>` [channels, conv], the norm
+    weights `<name><norm_suffix>`."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    conv: int
+    eps: float
+    position: Optional[RotarySpec] = None
+    scale: Optional[float] = None
+    chunk: Optional[int] = None
+    window: Optional[int] = None
+    weighting: str = "sigmoid"
+    head_bias: bool = True
+    gate: bool = True
+    bias: bool = True
+    out_bias: bool = True
+    names: Tuple[str, ...] = ("q", "k", "g", "o", "pb")
+    bias_suffix: str = ".b"
+    conv_suffix: str = ".conv"
+    norm_suffix: str = ".norm"
+    kind: str = "conv_attention"
+
+
+@dataclass(frozen=True)
+class TokenShiftSpec:
+    """A mixer whose input is first mixed with the token before: h_t <- h_t + (h_(t-1) - h_t) * mu, element by element,
+    h_(t-1) the input row of the sequence's token before as it was BEFORE this replacement (zeros before the first
+    token); the last row of a request is part of its state.  `inner`: the mixer's description; its tensors lie under
+    `inner_prefix`, mu [hidden] is `tensor`."""
+    inner: object
+    hidden_size: int
+    tensor: str = "shift"
+    inner_prefix: str = "mix."
+    kind: str = "token_shift"
+
+
+@dataclass(frozen=True)
 class ParallelMixerSpec:
     """Two mixers side by side on the same input: left_scale * left(h) + right_scale * right(h).  Each keeps its own
     cache or state; their tensors lie under `prefixes`."""
@@ -285,8 +343,8 @@ class SwiGLUSpec:
 @dataclass(frozen=True)
 class BlockSpec:
     """kind "pre_norm": x += mixer(norm1(x)); x += ffn(norm2(x)).
-    kind "post_norm": x += norm1(mixer(x)); x += norm2(ffn(x)): the sub-layers read the stream itself and
-    their OUTPUTS are normed; `ffn` may be None (the block is then its mixer alone, and norm2 is unused).
+    kind "post_norm": x += m norm1(mixer(x)); x += m norm2(ffn(x)), m = `residual_mult`: the sub-layers read the stream
+    itself and their OUTPUTS are normed; `ffn` may be None (the block is then its mixer alone, and norm2 is unused).
     kind "hyper_connection": `streams` copies x_1..x_S of the stream (all equal to the single stream when the first
     such block meets it); sub-layer q reads u = sum_s in_q[s] x_s through its norm and writes
     x_t <- sum_s mix_q[s, t] x_s + out_q[t] y; the single stream is the sum of the copies.  `hyper`: the two
@@ -299,6 +357,7 @@ class BlockSpec:
     streams: int = 1
     hyper: Optional[Tuple[object, object]] = None
     hyper_prefixes: Tuple[str, str] = ("hc1.", "hc2.")
+    residual_mult: float = 1.0      # post_norm: the factor on every normed sub-layer output
     # tensor-name prefixes of the four parts inside a layer (norm1, mixer, norm2, feed-forward)
     names: Tuple[str, str, str, str] = ("input_layernorm.", "self_attn.", "post_attention_layernorm.", "mlp.")
 
