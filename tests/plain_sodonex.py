@@ -66,28 +66,44 @@ def chunk_visible(i, j, size):
     return j <= i and i // size == j // size
 
 
+def whole_row_norm(u, w, eps):
+    """u [T, C] divided by the root mean square of the WHOLE row (all heads at once), times a weight per channel."""
+    return unit_rms(u, eps) * w.to(F)
+
+
+def sigmoid_chunk_weights(q, k, v, pb, scale, size):
+    """q [T, H, D], k and v [T, G, D], pb [H].  Every visible key weighs sigmoid(scale q.k + pb[head]) by itself;
+    nothing is divided by a sum.  Returns [T, H, D]."""
+    T, H, D = q.shape
+    G = k.shape[1]
+    out = torch.zeros(T, H, v.shape[2], dtype=F)
+    for t in range(T):
+        keys = [j for j in range(t + 1) if chunk_visible(t, j, size)]
+        for hd in range(H):
+            g = hd // (H // G)
+            s = (k[keys, g] @ q[t, hd]) * scale
+            w = torch.sigmoid(s + pb[hd].to(F))
+            out[t, hd] = (w[:, None] * v[keys, g]).sum(0)
+    return out
+
+
+def head_gate(o, h, wg):
+    """o [T, H, D] times sigmoid(W_g h), one number per head."""
+    return o * torch.sigmoid(lin(wg, h))[:, :, None]
+
+
 def sigmoid_attention(h, p, m, eps):
     """p: the mixer's tensors (q, q.b, k, k.b, q.conv, k.conv, q.norm, k.norm, pb, g, o, o.b); m: its sizes.
-    The values are the keys as they leave the convolution; every visible key weighs sigmoid(score + pb[head])."""
+    The values are the keys as they leave the convolution, before the norm and the rotation."""
     T = h.shape[0]
     H, G, D = m["heads"], m["kv_heads"], m["dim"]
     q = short_conv(lin(p["q"], h, p["q.b"]), p["q.conv"])
     k = short_conv(lin(p["k"], h, p["k.b"]), p["k.conv"])
     v = k.view(T, G, D)
-    q = (unit_rms(q, eps) * p["q.norm"].to(F)).view(T, H, D)
-    k = (unit_rms(k, eps) * p["k.norm"].to(F)).view(T, G, D)
-    q = rotate_half(q, m["rot"]["dims"], m["rot"]["base"])
-    k = rotate_half(k, m["rot"]["dims"], m["rot"]["base"])
-    gate = torch.sigmoid(lin(p["g"], h))                      # [T, H]
-    size = m["mask"]["size"]
-    out = torch.zeros(T, H, D, dtype=F)
-    for t in range(T):
-        keys = [j for j in range(t + 1) if chunk_visible(t, j, size)]
-        for hd in range(H):
-            g = hd // (H // G)
-            s = (k[keys, g] @ q[t, hd]) * m["scale"]
-            w = torch.sigmoid(s + p["pb"][hd].to(F))
-            out[t, hd] = (w[:, None] * v[keys, g]).sum(0) * gate[t, hd]
+    q = rotate_half(whole_row_norm(q, p["q.norm"], eps).view(T, H, D), m["rot"]["dims"], m["rot"]["base"])
+    k = rotate_half(whole_row_norm(k, p["k.norm"], eps).view(T, G, D), m["rot"]["dims"], m["rot"]["base"])
+    out = sigmoid_chunk_weights(q, k, v, p["pb"], m["scale"], m["mask"]["size"])
+    out = head_gate(out, h, p["g"])
     return lin(p["o"], out.reshape(T, H * D), p["o.b"])
 
 
