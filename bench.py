@@ -429,7 +429,8 @@ TIMED_OPS = ("paged_attention", "flash_prefill", "flash_prefill_tc5", "flash_dec
              "gemm_grouped_fused", "gemm_grouped_tc5", "gemm_bf16_small_m", "gemm_bf16_tc5", "gemm_bf16_tc5_pair", "layernorm_add",
              "layernorm_rows", "add_rmsnorm", "latent_norm_write", "qk_norm_rope_write", "moe_route", "moe_align",
              "moe_gather", "moe_combine", "gated_act", "silu_mul", "scale_softcap", "embed", "cast", "add_bias",
-             "hc_step", "dyt_rows", "short_conv", "ssd_scan", "mlstm_scan", "delta_scan", "gate_norm", "scaled_sum")
+             "hc_step", "dyt_rows", "short_conv", "ssd_scan", "mlstm_scan", "delta_scan", "gate_norm", "scaled_sum",
+             "token_shift", "rows_norm_rope_write", "rmsnorm_add", "unary_act")
 
 
 def kikepel_config(size, layers):
@@ -683,6 +684,129 @@ def tuzisun_bench(args):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------------
+# --sodonex: the Sodonex decoder (token shift, attention behind short convolutions with the keys as values, sigmoid
+# weights in blocks of positions, a gate per head; experts without a gate; post-norm blocks with a factor) beside the
+# Qwen3 decoder at equal width, depth, heads and active feed-forward width
+# ---------------------------------------------------------------------------------------------------
+# name: (width, heads, kv heads, head size, taps, positions per block of the mask, rotated features, expert ff, experts, top, vocab)
+SODONEX_SIZES = {"2k": (2048, 16, 4, 128, 4, 1024, 64, 1024, 32, 4, 65536),
+                 "4k": (4096, 32, 8, 128, 4, 2048, 64, 1408, 64, 6, 65536),
+                 "4k-h64": (4096, 64, 8, 64, 3, 512, 32, 2048, 32, 4, 65536)}
+
+
+def sodonex_config(size, layers):
+    W, H, KV, D, taps, block, rot, eff, E, top, vocab = SODONEX_SIZES[size]
+    mix = dict(heads=H, kv_heads=KV, dim=D, vdim=D, conv=taps, scale=D ** -0.5, mask=dict(size=block), rot=dict(dims=rot, base=500000.0))
+    moe = dict(kind="moe", expert=dict(ff=eff), router=dict(experts=E, top=top))
+    return dict(architecture="Sodonex", vocab=vocab, width=W, norm=dict(eps=1e-6), embedding=dict(scale=W ** 0.5), residual_mult=0.5,
+                max_position_embeddings=16384, layers=[dict(type="attention", mixer=mix, mlp=moe) for _ in range(layers)])
+
+
+def sodonex_bench(args):
+    import torch
+    from vllm_lite_b200.engine import LLMEngine, StepEntry, random_model
+    size, layers = args.sodonex, args.layers or 8
+    W, H, KV, D, taps, block, rot, eff, E, top, vocab = SODONEX_SIZES[size]
+    context, pk = args.context, peaks()
+    warmup = max(args.warmup, 3)
+    qwen = dict(QWEN3_8B, num_hidden_layers=layers, hidden_size=W, num_attention_heads=H, num_key_value_heads=KV,
+                head_dim=D, intermediate_size=top * eff, vocab_size=vocab, max_position_embeddings=16384)
+    results = {}
+    for name, cfg in (("sodonex", sodonex_config(size, layers)), ("qwen3", qwen)):
+        _, plan, weights = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+        slack = 256
+        pages = 64 * (-(-(context + slack) // args.block_size) + 1) + PREFILL_TOKENS // args.block_size + 64
+        engine = LLMEngine(plan=plan, weights=weights, dtype="bfloat16", kv_blocks=pages, block_size=args.block_size,
+                           max_batch_size=64, max_num_batched_tokens=PREFILL_TOKENS, prefill_chunk_size=PREFILL_TOKENS,
+                           max_model_len=context + slack)
+        del weights
+        runner, sampler = engine.runner, engine.sampler
+        for t in runner.storage.paged:
+            t.normal_()
+        res = {}
+        pms = prefill_run(runner, vocab)
+        res["prefill"] = {"tokens": PREFILL_TOKENS, "ms": round(pms, 3), "tokens_per_s": round(PREFILL_TOKENS / pms * 1e3, 1)}
+        for b in (8, 64):
+            ms, launches, _ = decode_run(runner, sampler, b, context, warmup, args.steps, "random", vocab, f"d{b}.")
+            res[f"decode_b{b}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(b * 1e3 / ms, 1), "launches": round(launches)}
+        gen = torch.Generator().manual_seed(5)
+        prompt = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
+        res["kernels_prefill"] = timed_step(runner, [StepEntry("kp", prompt, [PREFILL_TOKENS - 1])])
+        runner.release("kp")
+        ids = [f"kd{i}" for i in range(64)]
+        for rid in ids:
+            runner.cache.admit(rid)
+            runner.cache.append(rid, context - 1)
+        runner.storage.zero_slots(runner.cache.take_fresh_slots())
+        res["kernels_decode_b64"] = timed_step(runner, [StepEntry(rid, [i], [0]) for i, rid in enumerate(ids)])
+        for rid in ids:
+            runner.release(rid)
+        runner.check_device_errors()
+        res["weights_GB"] = round(sum(p.numel() * p.element_size() for p in _tensors_of(runner.model)) / 1e9, 2)
+        results[name] = res
+        del engine, runner, sampler
+        torch.cuda.empty_cache()
+    # ---- the new kernels against their rooflines, beside the like kernels of the closest model ---------
+    T, B = PREFILL_TOKENS, 64
+    sx, q = results["sodonex"], results["qwen3"]
+    def us(res, step, names):
+        return sum(res[step].get(n, [0, 0.0])[1] for n in names)
+    def count(res, step, name):
+        return res[step].get(name, [0, 0.0])[0]
+    tf = lambda flops, micro: round(flops / (micro * 1e-6) / 1e12, 1) if micro else None
+    gb = lambda nbytes, micro: round(nbytes / (micro * 1e-6) / 1e9, 1) if micro else None
+    att = ("paged_attention", "flash_prefill", "flash_prefill_tc5", "flash_decode")
+    keys_block = sum(p % block + 1 for p in range(T))              # keys all queries of the prompt read: their block up to themselves
+    keys_all = T * (T + 1) // 2
+    reach = (context - 1) % block + 1                              # keys a decoded token at the last position reads
+    roof = {}
+    roof["attention_prefill_tflops"] = {
+        "sodonex": tf(layers * 4.0 * H * D * keys_block, us(sx, "kernels_prefill", att)),
+        "qwen3": tf(layers * 4.0 * H * D * keys_all, us(q, "kernels_prefill", att)),
+        "us_a_layer": {"sodonex": round(us(sx, "kernels_prefill", att) / layers, 1), "qwen3": round(us(q, "kernels_prefill", att) / layers, 1)}}
+    roof["attention_decode_gbs"] = {
+        "sodonex": gb(layers * B * reach * 2.0 * KV * D * 2.0, us(sx, "kernels_decode_b64", att)),
+        "qwen3": gb(layers * B * context * 2.0 * KV * D * 2.0, us(q, "kernels_decode_b64", att)),
+        "keys_a_token": {"sodonex": reach, "qwen3": context},
+        "us_a_layer": {"sodonex": round(us(sx, "kernels_decode_b64", att) / layers, 1), "qwen3": round(us(q, "kernels_decode_b64", att) / layers, 1)}}
+    C = (H + KV) * D
+    for step, rows in (("kernels_prefill", T), ("kernels_decode_b64", B)):
+        r = {}
+        # token shift: the float32 stream in, the activation out
+        r["token_shift_gbs"] = gb(count(sx, step, "token_shift") * rows * W * 6.0, us(sx, step, ("token_shift",)))
+        # convolution: the projection's q and k columns in (bfloat16), float32 out
+        r["short_conv_gbs"] = gb(count(sx, step, "short_conv") * rows * C * 6.0, us(sx, step, ("short_conv",)))
+        # whole-row norm, rotation, cache write: float32 q and k in; q, k and v out in bfloat16
+        r["rows_norm_rope_write_gbs"] = gb(count(sx, step, "rows_norm_rope_write") * rows * (C * 4.0 + (H + 2 * KV) * D * 2.0),
+                                           us(sx, step, ("rows_norm_rope_write",)))
+        r["qwen3_qk_norm_rope_write_gbs"] = gb(count(q, step, "qk_norm_rope_write") * rows * (H + 2 * KV) * D * 4.0,
+                                               us(q, step, ("qk_norm_rope_write",)))
+        # norm of a sublayer's output added into the stream: y in, x in and out, cast out
+        r["rmsnorm_add_gbs"] = gb(count(sx, step, "rmsnorm_add") * rows * W * 12.0, us(sx, step, ("rmsnorm_add",)))
+        r["qwen3_add_rmsnorm_gbs"] = gb(count(q, step, "add_rmsnorm") * rows * W * 12.0, us(q, step, ("add_rmsnorm",)))
+        roof[step] = r
+    grouped = ("gemm_grouped", "gemm_grouped_fused", "gemm_grouped_tc5")
+    q_layer = (H + 2 * KV) * D * W + W * H * D + 3 * W * top * eff          # matrix elements of a Qwen3 layer
+    roof["expert_products_prefill_tflops"] = {
+        "sodonex": tf(layers * 2.0 * T * top * 2 * W * eff, us(sx, "kernels_prefill", grouped)),
+        "qwen3 (all dense products of the layers)": tf(layers * 2.0 * T * q_layer,
+                                                       us(q, "kernels_prefill", ("gemm_bf16_tc5", "gemm_bf16_tc5_pair", "library_mm")))}
+    touched = min(E, B * top)
+    roof["expert_products_decode_gbs"] = {
+        "sodonex (experts that 64 tokens can reach)": gb(layers * touched * 2.0 * W * eff * 2, us(sx, "kernels_decode_b64", grouped)),
+        "qwen3 (all products)": gb(q["weights_GB"] * 1e9 - 2.0 * vocab * W * 2, us(q, "kernels_decode_b64", ("library_mm", "gemm_bf16_small_m")))}
+    roof["peaks"] = {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "source": pk["source"]}
+    print(json.dumps({"sodonex_bench": size, "layers": layers, "context": context, "steps": args.steps, "warmup": warmup,
+                      "dtype": "bf16", "data": "synthetic (random weights, uniform token ids)",
+                      "config": {"sodonex": dict(zip(("width", "heads", "kv_heads", "dim", "taps", "mask_block", "rotated", "expert_ff",
+                                                      "experts", "top", "vocab"), SODONEX_SIZES[size])),
+                                 "qwen3": {k_: qwen[k_] for k_ in ("hidden_size", "num_attention_heads", "num_key_value_heads",
+                                                                    "head_dim", "intermediate_size", "vocab_size")}},
+                      "results": results, "roofline": roof}))
+    return 0
+
+
 def _tensors_of(model):
     """Every device tensor that the parts of a model hold (weights as they are resident)."""
     import torch
@@ -729,6 +853,9 @@ def main(argv=None):
                     help="instead of the default workload: the Tuzisun decoder at layer sizes " + ", ".join(sorted(TUZISUN_SIZES))
                          + " beside the Qwen3 decoder at equal width, depth and heads: prefill of 2,048 tokens, decode at batch 8 "
                            "and 64, and every kernel of a step between CUDA events (--layers, default 8; --context, --steps)")
+    ap.add_argument("--sodonex", default=None, choices=sorted(SODONEX_SIZES), metavar="SIZE",
+                    help="instead of the default workload: the Sodonex decoder at layer sizes " + ", ".join(sorted(SODONEX_SIZES))
+                         + " beside the Qwen3 decoder at equal width, depth, heads and active feed-forward width")
     ap.add_argument("--kikepel", default=None, choices=sorted(KIKEPEL_SIZES), metavar="SIZE",
                     help="instead of the default workload: the Kikepel decoder at layer sizes " + ", ".join(sorted(KIKEPEL_SIZES))
                          + " beside the Qwen3 decoder at equal width, depth and heads: prefill of 2,048 tokens, decode at batch 8 "
@@ -747,6 +874,8 @@ def main(argv=None):
         return kikepel_bench(args)
     if args.tuzisun:
         return tuzisun_bench(args)
+    if args.sodonex:
+        return sodonex_bench(args)
     import torch
     from vllm_lite_b200.csrc import ops
     from vllm_lite_b200.engine import LLMEngine, random_model

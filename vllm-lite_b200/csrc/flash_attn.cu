@@ -18,6 +18,11 @@
 //   chunks of a token are merged by the blocks of a cluster (up to 16), by the block that arrives
 //   last, or (scratch layout of vl_decode_attention) by vl_decode_attention_merge.
 // vl_flash_decode_fused: the same, doing the step's head norm, rotation and cache write on the way.
+// Options of the prefill kernel and of the block-per-chunk decode kernel (as in csrc/attention.cu): `block` > 0 cuts a
+// request's positions into blocks of that many, counted from its first token, and a query reads no key of an earlier
+// block; `gate` multiplies head h's output for token t by sigmoid(gate[t * gate_stride + h]); the weighting SIG
+// replaces the softmax: a visible key weighs sigmoid(s_j + head_bias[h]) by itself, nothing is divided by a sum, and
+// partial results of chunks and warps simply add up (they travel with a maximum of 0, so every merge weighs them 1).
 // Rows of shared-memory tiles are padded by 16 bytes, which makes every 8-row ldmatrix access
 // hit 8 different banks groups for any head size.
 #include "rope_head.cuh"
@@ -61,6 +66,22 @@ __device__ __forceinline__ float exp2_mufu(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+// 1 / (1 + 2^(-x)) for x in units of log2: the sigmoid of x ln 2 (x = -inf gives 0, x = +inf gives 1)
+__device__ __forceinline__ float sigmoid_log2(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(1.f + exp2_mufu(-x)));
+    return y;
+}
+// What the options of a launch add to its arguments: the mask's blocks, the sigmoid's bias per head, the output gate.
+struct AttnOptions {
+    int weighting;                                       // 0: softmax, 1: sigmoid (picks the kernel; the same numbers as csrc/attention.cu)
+    int block;                                           // positions per block of the mask (0: none)
+    const float* head_bias;                              // (SIG) a number per query head added to every score, or null
+    const bf16* gate; int gate_stride;                   // a gate logit per (token of the step, head), or null
+};
+__device__ __forceinline__ float gate_factor(const AttnOptions& op, int tok, int h) {
+    return op.gate ? 1.f / (1.f + __expf(-__bfloat162float(op.gate[(size_t)tok * op.gate_stride + h]))) : 1.f;
 }
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -107,12 +128,13 @@ __device__ __forceinline__ float sink_inverse_log2(float m, float l, float sink)
 
 // tiles[i] = {row of the block table, index of the tile's first token in the step, tokens, position of the first};
 // blocks (h, y) serve head h and, of the list walked from its end, the tokens 64 * (y' % parts) ... of tile y' / parts
-extern "C" __global__ void __launch_bounds__(NTHREADS)
+template <bool SIG>
+__global__ void __launch_bounds__(NTHREADS)
 flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                      const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                      const int* __restrict__ block_table, int max_blocks, const int4* __restrict__ tiles, int parts,
                      int nq, int nkv, int page_size, int num_pages, float scale_log2, int window, unsigned* err,
-                     const float* __restrict__ sinks) {
+                     const float* __restrict__ sinks, AttnOptions op) {
     extern __shared__ __align__(128) unsigned char fa_smem[];
     bf16* Qs = reinterpret_cast<bf16*>(fa_smem);                 // [BM][LDS]
     bf16* Ks = Qs + BM * LDS;                                    // [2][BN][LDS]
@@ -129,7 +151,9 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int* table = block_table + (size_t)req * max_blocks;
     const int hi = pos0 + count - 1;                             // the last key any row reads
-    const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    if (op.block > 0) lo = max(lo, pos0 / op.block * op.block);  // the first row's block starts first
+    const int blk_hi = op.block > 0 ? hi / op.block * op.block : 0;     // where the last row's block starts
     const int kt_lo = lo / BN, kt_hi = hi / BN;
 
     for (int idx = tid; idx < BM * CPR; idx += NTHREADS) {       // the query tile (rows beyond count: zeros)
@@ -153,6 +177,8 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     const int row0 = warp * 16;                                  // this warp's rows of the tile
     const int pos_a = pos0 + row0 + g, pos_b = pos_a + 8;        // positions of the lane's two rows
     const bool row_a = row0 + g < count, row_b = row0 + g + 8 < count;
+    const int blk_a = op.block > 0 ? pos_a / op.block * op.block : 0, blk_b = op.block > 0 ? pos_b / op.block * op.block : 0;
+    const float bias_log2 = (SIG && op.head_bias) ? op.head_bias[h] * 1.4426950408889634f : 0.f;
 
     for (int kt = kt_lo; kt <= kt_hi; ++kt) {
         const int buf = (kt - kt_lo) & 1;
@@ -190,7 +216,7 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
         // mask and online softmax.  The running maximum is kept in units of log2 (score * scale * log2 e);
         // the scale is applied inside the exponent: p = 2^(s * scale_log2 - base).
         const int j_base = kt * BN + 2 * t;
-        const bool need_mask = (kt * BN + BN - 1 > pos0 + row0) || (window > 0) || !row_a || !row_b;
+        const bool need_mask = (kt * BN + BN - 1 > pos0 + row0) || (window > 0) || !row_a || !row_b || kt * BN < blk_hi;
         float mx[2] = {-INFINITY, -INFINITY};
         if (need_mask) {
 #pragma unroll
@@ -200,10 +226,31 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
                     const int j = j_base + n * 8 + (e & 1);
                     const int p = (e < 2) ? pos_a : pos_b;
                     const bool rv = (e < 2) ? row_a : row_b;
-                    if (!rv || j > p || (window > 0 && j <= p - window)) s[n][e] = -INFINITY;
+                    if (!rv || j > p || (window > 0 && j <= p - window) || j < ((e < 2) ? blk_a : blk_b)) s[n][e] = -INFINITY;
                 }
             }
         }
+        if constexpr (SIG) {
+            // every key by itself: its weight in float32, rounded to bfloat16 for the second product like a probability
+            unsigned pf[BN / 16][4];
+#pragma unroll
+            for (int n = 0; n < BN / 8; ++n) {
+                const float p0 = sigmoid_log2(fmaf(s[n][0], scale_log2, bias_log2)), p1 = sigmoid_log2(fmaf(s[n][1], scale_log2, bias_log2));
+                const float p2 = sigmoid_log2(fmaf(s[n][2], scale_log2, bias_log2)), p3 = sigmoid_log2(fmaf(s[n][3], scale_log2, bias_log2));
+                pf[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);
+                pf[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
+            }
+#pragma unroll
+            for (int kb16 = 0; kb16 < BN / 16; ++kb16) {
+#pragma unroll
+                for (int dp = 0; dp < DTILES / 2; ++dp) {
+                    unsigned vb[4];
+                    ldmatrix_x4_trans(vb, Vt + (size_t)(kb16 * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + dp * 16 + 8 * (lane >> 4));
+                    mma16816(o[2 * dp], pf[kb16], vb[0], vb[1]);
+                    mma16816(o[2 * dp + 1], pf[kb16], vb[2], vb[3]);
+                }
+            }
+        } else {
 #pragma unroll
         for (int n = 0; n < BN / 8; ++n) {
             mx[0] = fmaxf(mx[0], fmaxf(s[n][0], s[n][1]));
@@ -250,6 +297,7 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
                 mma16816(o[2 * dp + 1], pf[kb16], vb[2], vb[3]);
             }
         }
+        }                                                        // (softmax)
         __syncthreads();                                         // the tile may be overwritten next round
     }
 #pragma unroll
@@ -263,6 +311,9 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
         inv_a = sink_inverse_log2(m_run[0], l_run[0], sk);
         inv_b = sink_inverse_log2(m_run[1], l_run[1], sk);
     }
+    if constexpr (SIG) inv_a = inv_b = 1.f;                      // nothing is divided by a sum
+    if (row_a) inv_a *= gate_factor(op, tok0 + row0 + g, h);
+    if (row_b) inv_b *= gate_factor(op, tok0 + row0 + g + 8, h);
     if (row_a) {
         bf16* op = out + ((size_t)(tok0 + row0 + g) * nq + h) * HD + 2 * t;
 #pragma unroll
@@ -280,19 +331,24 @@ extern "C" int vl_flash_head_dim() { return HD; }
 extern "C" int vl_flash_prefill(const void* q, int q_stride, void* out, const void* kcache, const void* vcache,
                                 const int* block_table, int max_blocks, const int* tiles, int num_tiles, int tile_rows,
                                 int nq, int nkv, int hd, int page_size, int num_pages, float scale, int window,
-                                unsigned* err, const float* sinks, void* stream) {
+                                unsigned* err, const float* sinks, int weighting, int block, const float* head_bias,
+                                const void* gate, int gate_stride, void* stream) {
     if (num_tiles <= 0) return VL_OK;
     if (hd != HD) return VL_ERR_UNSUPPORTED;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || q_stride % 8) return VL_ERR_ARGUMENT;
     if (tile_rows <= 0 || tile_rows > 65536) return VL_ERR_ARGUMENT;
+    if (weighting < 0 || weighting > 1 || block < 0 || (gate && gate_stride < nq) || (weighting == 1 && sinks)) return VL_ERR_ARGUMENT;
+    if (weighting == 0 && head_bias) return VL_ERR_ARGUMENT;
     const int parts = (tile_rows + BM - 1) / BM;                 // blocks per tile of the list
     if ((long long)num_tiles * parts > 65535) return VL_ERR_UNSUPPORTED;
     const size_t smem = (size_t)(BM + 4 * BN) * LDS * sizeof(bf16);
-    cudaError_t e = cudaFuncSetAttribute(flash_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    auto kernel = weighting == 1 ? flash_prefill_kernel<true> : flash_prefill_kernel<false>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    flash_prefill_kernel<<<dim3(nq, num_tiles * parts), NTHREADS, smem, (cudaStream_t)stream>>>(
+    const AttnOptions op = {weighting, block, head_bias, (const bf16*)gate, gate_stride};
+    kernel<<<dim3(nq, num_tiles * parts), NTHREADS, smem, (cudaStream_t)stream>>>(
         (const bf16*)q, q_stride, (bf16*)out, (const bf16*)kcache, (const bf16*)vcache, block_table, max_blocks,
-        (const int4*)tiles, parts, nq, nkv, page_size, num_pages, scale * 1.4426950408889634f, window, err, sinks);
+        (const int4*)tiles, parts, nq, nkv, page_size, num_pages, scale * 1.4426950408889634f, window, err, sinks, op);
     return vl_launch_status();
 }
 
@@ -328,9 +384,10 @@ constexpr int DEC_MAX_CLUSTER = 16;                  // most chunks of a token t
 // result in its shared memory (bO [rows][HD], bM maxima in units of log2, bL sums); block `rank` of
 // the S merges an S-th of the elements, the chunks in their order, through the cluster's shared
 // window, and writes them to the output rows.
+template <typename Finish>
 __device__ __forceinline__ void decode_cluster_merge(const float* bO, const float* bM, const float* bL, bf16* out,
                                                      int tok, int nq, int h0, int nvalid, int S, int rank, int tid,
-                                                     const float* sinks) {
+                                                     Finish finish) {
     __syncthreads();
     dec_cluster_sync();
     unsigned aO[DEC_MAX_CLUSTER], aM[DEC_MAX_CLUSTER], aL[DEC_MAX_CLUSTER];
@@ -362,8 +419,7 @@ __device__ __forceinline__ void decode_cluster_merge(const float* bO, const floa
             L += l[s] * wgt;
             acc += a[s] * wgt;
         }
-        const float inv = sinks ? sink_inverse_log2(M, L, sinks[h0 + r] * 1.4426950408889634f) : (L > 0.f ? 1.0f / L : 0.f);
-        out[((size_t)tok * nq + h0 + r) * HD + (idx - r * HD)] = __float2bfloat16(acc * inv);
+        out[((size_t)tok * nq + h0 + r) * HD + (idx - r * HD)] = __float2bfloat16(acc * finish(M, L, h0 + r));
     }
     dec_cluster_sync();                                          // no block leaves while another may still read its result
 }
@@ -383,13 +439,22 @@ struct DecodeFusion {
     bf16* kcache; bf16* vcache;                          // the cache again, to write
     int on;
     const float* sinks;                                  // (any launch) a sink per query head for the softmax, or null
+    AttnOptions op;                                      // (any launch) blocks of the mask, the sigmoid's bias, the output gate
 };
+// The factor that turns a token's merged sums (maximum M in units of log2, sum L) into head h's output row.
+template <bool SIG>
+__device__ __forceinline__ float decode_finish(const DecodeFusion& fz, float M, float L, int tok, int h) {
+    float inv = 1.f;                                             // (SIG) nothing is divided by a sum
+    if constexpr (!SIG)
+        inv = fz.sinks ? sink_inverse_log2(M, L, fz.sinks[h] * 1.4426950408889634f) : (L > 0.f ? 1.0f / L : 0.f);
+    return inv * gate_factor(fz.op, tok, h);
+}
 
 // TR: the products are taken the other way round, S^T = K Q^T and O^T = V^T P^T: the 16 keys of a warp's tile are
 // the 16 rows of the tensor-core tile and the query heads of the KV head its 8 columns (for groups of up
 // to 8 heads; with heads as rows, 16 of them, a group of 4 wastes three quarters of every product): half the
 // products, half the accumulators and half the exponentials per key.
-template <bool TR>
+template <bool TR, bool SIG>
 __global__ void __launch_bounds__(NTHREADS)
 flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
                     const bf16* kcache, const bf16* vcache,
@@ -434,7 +499,9 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
         }
         return;
     }
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    if (fz.op.block > 0) lo = max(lo, pos / fz.op.block * fz.op.block);
+    auto finish = [&](float M, float L, int h) { return decode_finish<SIG>(fz, M, L, tok, h); };
     const int c0 = max(split * chunk, lo);
     const int c1 = min((split + 1) * chunk, pos + 1);
     // (in_cluster) the blocks of a cluster serve one token: they all see the same `alone`
@@ -445,7 +512,7 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
         pdl_wait();                                              // the merge writes output rows
         for (int i = tid; i < nvalid * HD; i += NTHREADS) bO[i] = 0.f;
         if (tid < DEC_ROWS) { s_bm[tid] = -INFINITY; s_bl[tid] = 0.f; }
-        decode_cluster_merge(bO, s_bm, s_bl, out, tok, nq, h0, nvalid, S, split, tid, fz.sinks);
+        decode_cluster_merge(bO, s_bm, s_bl, out, tok, nq, h0, nvalid, S, split, tid, finish);
         return;
     }
     const int* table = block_table + (size_t)req_index[tok] * max_blocks;
@@ -548,7 +615,12 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
     if constexpr (TR) {
         // ---- keys as rows: lane (g, t) holds keys g and g + 8 of the tile and heads 2t, 2t + 1 ----
         constexpr int MT = HD / 16;                              // tiles of 16 features of the output
-        float oT[MT][4], m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+        float oT[MT][4], m_run[2] = {SIG ? 0.f : -INFINITY, SIG ? 0.f : -INFINITY}, l_run[2] = {0.f, 0.f};
+        float hb[2] = {0.f, 0.f};                                // (SIG) the bias of heads 2t and 2t + 1, in units of log2
+        if (SIG && fz.op.head_bias) {
+            hb[0] = fz.op.head_bias[h0 + min(2 * t, nvalid - 1)] * 1.4426950408889634f;
+            hb[1] = fz.op.head_bias[h0 + min(2 * t + 1, nvalid - 1)] * 1.4426950408889634f;
+        }
 #pragma unroll
         for (int d = 0; d < MT; ++d) { oT[d][0] = oT[d][1] = oT[d][2] = oT[d][3] = 0.f; }
         unsigned qb[KSTEPS][2];                                  // Q^T as the 16 x 8 operand: features 2t.., 2t + 8.. of head g
@@ -579,22 +651,28 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
             const bool in0 = j0 >= c0 && j0 < c1, in1 = j0 + 8 >= c0 && j0 + 8 < c1;
             sT[0] = in0 ? sT[0] * scale_log2 : -INFINITY; sT[1] = in0 ? sT[1] * scale_log2 : -INFINITY;
             sT[2] = in1 ? sT[2] * scale_log2 : -INFINITY; sT[3] = in1 ? sT[3] * scale_log2 : -INFINITY;
-            float mx[2] = {fmaxf(sT[0], sT[2]), fmaxf(sT[1], sT[3])}, corr[2], base[2];
+            float corr[2] = {1.f, 1.f}, p0, p1, p2, p3;
+            if constexpr (SIG) {                                 // every key by itself; the sums stay relative to 0
+                p0 = sigmoid_log2(sT[0] + hb[0]); p1 = sigmoid_log2(sT[1] + hb[1]);
+                p2 = sigmoid_log2(sT[2] + hb[0]); p3 = sigmoid_log2(sT[3] + hb[1]);
+            } else {
+                float mx[2] = {fmaxf(sT[0], sT[2]), fmaxf(sT[1], sT[3])}, base[2];
 #pragma unroll
-            for (int r = 0; r < 2; ++r) {                        // over the 16 keys: the lanes of equal t
-                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 4));
-                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 8));
-                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 16));
-                const float mn = fmaxf(m_run[r], mx[r]);
-                base[r] = (mn == -INFINITY) ? 0.f : mn;
-                corr[r] = exp2_mufu(m_run[r] - base[r]);
-                m_run[r] = mn;
-                l_run[r] *= corr[r];
+                for (int r = 0; r < 2; ++r) {                    // over the 16 keys: the lanes of equal t
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 4));
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 8));
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 16));
+                    const float mn = fmaxf(m_run[r], mx[r]);
+                    base[r] = (mn == -INFINITY) ? 0.f : mn;
+                    corr[r] = exp2_mufu(m_run[r] - base[r]);
+                    m_run[r] = mn;
+                    l_run[r] *= corr[r];
+                }
+                p0 = exp2_mufu(sT[0] - base[0]); p1 = exp2_mufu(sT[1] - base[1]);
+                p2 = exp2_mufu(sT[2] - base[0]); p3 = exp2_mufu(sT[3] - base[1]);
+                l_run[0] += p0 + p2;
+                l_run[1] += p1 + p3;
             }
-            const float p0 = exp2_mufu(sT[0] - base[0]), p1 = exp2_mufu(sT[1] - base[1]);
-            const float p2 = exp2_mufu(sT[2] - base[0]), p3 = exp2_mufu(sT[3] - base[1]);
-            l_run[0] += p0 + p2;
-            l_run[1] += p1 + p3;
             // P^T as the 16 x 8 operand of the second product: keys 2t.., 2t + 8.. of head g = the transposes of
             // the two 8 x 8 blocks (keys g | g + 8, heads 2t..) that this lane's probabilities are rows of
             unsigned pb0, pb1;
@@ -604,7 +682,7 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
             for (int d = 0; d < MT; ++d) {
                 unsigned va[4];                                  // V^T: features 16 d + (g | g + 8) x keys (2t.. | 2t + 8..)
                 ldmatrix_x4_trans(va, Vt + (size_t)((lane & 7) + 8 * (lane >> 4)) * LDS + d * 16 + 8 * ((lane >> 3) & 1));
-                oT[d][0] *= corr[0]; oT[d][1] *= corr[1]; oT[d][2] *= corr[0]; oT[d][3] *= corr[1];
+                if constexpr (!SIG) { oT[d][0] *= corr[0]; oT[d][1] *= corr[1]; oT[d][2] *= corr[0]; oT[d][3] *= corr[1]; }
                 mma16816(oT[d], va, pb0, pb1);
             }
         }
@@ -627,7 +705,12 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
             s_m[warp][2 * t + 1] = m_run[1]; s_l[warp][2 * t + 1] = l_run[1];
         }
     } else {
-        float o[DTILES][4], m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+        float o[DTILES][4], m_run[2] = {SIG ? 0.f : -INFINITY, SIG ? 0.f : -INFINITY}, l_run[2] = {0.f, 0.f};
+        float hb[2] = {0.f, 0.f};                                    // (SIG) the bias of heads g and g + 8, in units of log2
+        if (SIG && fz.op.head_bias) {
+            hb[0] = fz.op.head_bias[h0 + min(g, nvalid - 1)] * 1.4426950408889634f;
+            hb[1] = fz.op.head_bias[h0 + min(g + 8, nvalid - 1)] * 1.4426950408889634f;
+        }
 #pragma unroll
         for (int d = 0; d < DTILES; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
         unsigned qf[KSTEPS][4];
@@ -665,19 +748,24 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
                     s[n][e] = v;
                     mx[e >> 1] = fmaxf(mx[e >> 1], v);
                 }
-            float corr[2], base[2];
-#pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-                const float mn = fmaxf(m_run[r], mx[r]);
-                base[r] = (mn == -INFINITY) ? 0.f : mn;
-                corr[r] = exp2_mufu(m_run[r] - base[r]);
-                m_run[r] = mn;
-                l_run[r] *= corr[r];
-            }
+            float corr[2] = {1.f, 1.f}, base[2] = {0.f, 0.f};
             unsigned pf[4];
-            {
+            if constexpr (SIG) {                                     // every key by itself; the sums stay relative to 0
+                pf[0] = pack_bf16(sigmoid_log2(s[0][0] + hb[0]), sigmoid_log2(s[0][1] + hb[0]));
+                pf[1] = pack_bf16(sigmoid_log2(s[0][2] + hb[1]), sigmoid_log2(s[0][3] + hb[1]));
+                pf[2] = pack_bf16(sigmoid_log2(s[1][0] + hb[0]), sigmoid_log2(s[1][1] + hb[0]));
+                pf[3] = pack_bf16(sigmoid_log2(s[1][2] + hb[1]), sigmoid_log2(s[1][3] + hb[1]));
+            } else {
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                    const float mn = fmaxf(m_run[r], mx[r]);
+                    base[r] = (mn == -INFINITY) ? 0.f : mn;
+                    corr[r] = exp2_mufu(m_run[r] - base[r]);
+                    m_run[r] = mn;
+                    l_run[r] *= corr[r];
+                }
                 const float p00 = exp2_mufu(s[0][0] - base[0]), p01 = exp2_mufu(s[0][1] - base[0]);
                 const float p02 = exp2_mufu(s[0][2] - base[1]), p03 = exp2_mufu(s[0][3] - base[1]);
                 const float p10 = exp2_mufu(s[1][0] - base[0]), p11 = exp2_mufu(s[1][1] - base[0]);
@@ -691,8 +779,10 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
             for (int dp = 0; dp < DTILES / 2; ++dp) {
                 unsigned vb[4];
                 ldmatrix_x4_trans(vb, Vt + (size_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + dp * 16 + 8 * (lane >> 4));
-                o[2 * dp][0] *= corr[0]; o[2 * dp][1] *= corr[0]; o[2 * dp][2] *= corr[1]; o[2 * dp][3] *= corr[1];
-                o[2 * dp + 1][0] *= corr[0]; o[2 * dp + 1][1] *= corr[0]; o[2 * dp + 1][2] *= corr[1]; o[2 * dp + 1][3] *= corr[1];
+                if constexpr (!SIG) {
+                    o[2 * dp][0] *= corr[0]; o[2 * dp][1] *= corr[0]; o[2 * dp][2] *= corr[1]; o[2 * dp][3] *= corr[1];
+                    o[2 * dp + 1][0] *= corr[0]; o[2 * dp + 1][1] *= corr[0]; o[2 * dp + 1][2] *= corr[1]; o[2 * dp + 1][3] *= corr[1];
+                }
                 mma16816(o[2 * dp], pf, vb[0], vb[1]);
                 mma16816(o[2 * dp + 1], pf, vb[2], vb[3]);
             }
@@ -729,9 +819,7 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
             L += s_l[w][r] * wgt;
         }
         if (alone) {                                             // nothing to merge with: the output row itself
-            const float inv = fz.sinks ? sink_inverse_log2(M, L, fz.sinks[h0 + r] * 1.4426950408889634f)
-                                       : (L > 0.f ? 1.0f / L : 0.f);
-            out[((size_t)tok * nq + h0 + r) * HD + e] = __float2bfloat16(acc * inv);
+            out[((size_t)tok * nq + h0 + r) * HD + e] = __float2bfloat16(acc * finish(M, L, h0 + r));
             continue;
         }
         if (in_cluster) {
@@ -748,7 +836,7 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
     }
     if (alone) return;
     if (in_cluster) {
-        decode_cluster_merge(bO, s_bm, s_bl, out, tok, nq, h0, nvalid, S, split, tid, fz.sinks);
+        decode_cluster_merge(bO, s_bm, s_bl, out, tok, nq, h0, nvalid, S, split, tid, finish);
         return;
     }
     if (!arrivals) return;                                       // the caller merges with a kernel of its own
@@ -793,11 +881,13 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
         L += __shfl_xor_sync(0xffffffffu, L, 2);
         L += __shfl_xor_sync(0xffffffffu, L, 4);
         if (part == 0) {
-            s_inv[r] = L > 0.f ? 1.0f / L : 0.f;
+            float inv = L > 0.f ? 1.0f / L : 0.f;
             if (fz.sinks) {                                      // natural-log units here
                 const float sk = fz.sinks[h0 + min(r, nvalid - 1)], Mx = fmaxf(M, sk), a = __expf(M - Mx);
-                s_inv[r] = a / (L * a + __expf(sk - Mx));
+                inv = a / (L * a + __expf(sk - Mx));
             }
+            if constexpr (SIG) inv = 1.f;                        // nothing is divided by a sum
+            s_inv[r] = inv * gate_factor(fz.op, tok, h0 + min(r, nvalid - 1));
         }
     }
     __syncthreads();
@@ -814,12 +904,25 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
 
 // The largest cluster the decode kernel may be launched as on this device: 16 where clusters beyond the
 // portable size are allowed and one fits, else 8.
+typedef void (*DecodeKernel)(const bf16*, int, const bf16*, const bf16*, const int*, int, const int*, const int*, int, int, int,
+                             int, float, int, int, int, float*, float*, unsigned*, const int*, bf16*, int*, int, DecodeFusion);
+// the kernel for (keys as rows, sigmoid weighting)
+static DecodeKernel decode_kernel(bool tr, bool sig) {
+    if (sig) return tr ? flash_decode_kernel<true, true> : flash_decode_kernel<false, true>;
+    return tr ? flash_decode_kernel<true, false> : flash_decode_kernel<false, false>;
+}
+static cudaError_t decode_kernels_attribute(cudaFuncAttribute attr, int value) {
+    for (int i = 0; i < 4; ++i) {
+        const cudaError_t e = cudaFuncSetAttribute(decode_kernel(i & 1, i & 2), attr, value);
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
 static int decode_max_cluster() {
     static int v = 0;
     if (!v) {
         v = 8;
-        if (cudaFuncSetAttribute(flash_decode_kernel<false>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess &&
-            cudaFuncSetAttribute(flash_decode_kernel<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+        if (decode_kernels_attribute(cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
             const size_t ring = (size_t)DEC_NST * 2 * BN * LDS * sizeof(bf16);
             const size_t merge = (size_t)(4 * DEC_ROWS * (HD + 4) + DEC_ROWS * HD) * sizeof(float);
             const size_t smem = (size_t)DEC_ROWS * LDS * sizeof(bf16) + (ring > merge ? ring : merge);
@@ -833,11 +936,10 @@ static int decode_max_cluster() {
             cfg.attrs = attr;
             cfg.numAttrs = 1;
             int clusters = 0;
-            if (cudaFuncSetAttribute(flash_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess &&
-                cudaFuncSetAttribute(flash_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess &&
-                cudaOccupancyMaxActiveClusters(&clusters, flash_decode_kernel<false>, &cfg) == cudaSuccess && clusters >= 8 &&
-                cudaOccupancyMaxActiveClusters(&clusters, flash_decode_kernel<true>, &cfg) == cudaSuccess && clusters >= 8)
-                v = 16;
+            bool all = decode_kernels_attribute(cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+            for (int i = 0; all && i < 4; ++i)
+                all = cudaOccupancyMaxActiveClusters(&clusters, decode_kernel(i & 1, i & 2), &cfg) == cudaSuccess && clusters >= 8;
+            if (all) v = 16;
         }
         cudaGetLastError();                                      // a refusal above is an answer, not an error of the step
     }
@@ -871,13 +973,17 @@ static int launch_flash_decode(const void* q, int q_stride, const void* kcache, 
     if (chunk <= 0 || chunk % BN || chunk > DEC_MAX_CHUNK || S <= 0 || S > 65535 || T > 65535) return VL_ERR_ARGUMENT;
     if ((out == nullptr) != (arrivals == nullptr)) return VL_ERR_ARGUMENT;
     if (arrivals && S > vl_flash_decode_own_merge_cap()) return VL_ERR_UNSUPPORTED;
+    const bool sig = fz.op.weighting == 1;
+    if (fz.op.weighting < 0 || fz.op.weighting > 1 || fz.op.block < 0 || (!sig && fz.op.head_bias)) return VL_ERR_ARGUMENT;
+    // the merge kernel that follows a launch without `out` knows neither the sigmoid nor the gate
+    if ((sig || fz.op.gate) && out == nullptr) return VL_ERR_UNSUPPORTED;
+    if ((sig && fz.sinks) || (fz.op.gate && fz.op.gate_stride < nq)) return VL_ERR_ARGUMENT;
     const int grp = nq / nkv;
     const int htiles = (grp + DEC_ROWS - 1) / DEC_ROWS;
     const size_t ring = (size_t)DEC_NST * 2 * BN * LDS * sizeof(bf16);
     const size_t merge = (size_t)(4 * DEC_ROWS * (HD + 4) + DEC_ROWS * HD) * sizeof(float);
     const size_t smem = (size_t)DEC_ROWS * LDS * sizeof(bf16) + (ring > merge ? ring : merge);
-    cudaError_t e = cudaFuncSetAttribute(flash_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = decode_kernels_attribute(cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     // A cluster starts when all its blocks find room at once: good while the whole grid is resident at
     // the same time (measured at 8 requests of 4,096 keys: 33.4 -> 29.5 us), a loss when blocks queue for
@@ -887,7 +993,7 @@ static int launch_flash_decode(const void* q, int q_stride, const void* kcache, 
         int dev = 0, sms = 0, per_sm = 0;
         cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, flash_decode_kernel<true>, NTHREADS, smem) != cudaSuccess || per_sm < 1)
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, flash_decode_kernel<true, false>, NTHREADS, smem) != cudaSuccess || per_sm < 1)
             per_sm = 1;
         resident = sms * per_sm;
     }
@@ -912,8 +1018,8 @@ static int launch_flash_decode(const void* q, int q_stride, const void* kcache, 
     cfg.attrs = attr;
     cfg.numAttrs = na;
     // groups of up to 8 query heads: keys as the rows of the tensor-core tiles, heads as their 8 columns
-    return (int)cudaLaunchKernelEx(&cfg, grp <= 8 ? flash_decode_kernel<true> : flash_decode_kernel<false>, (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache,
-                                   block_table, max_blocks, req_index, positions, nq, nkv, page_size, num_pages,
+    return (int)cudaLaunchKernelEx(&cfg, decode_kernel(grp <= 8, sig), (const bf16*)q, q_stride, (const bf16*)kcache,
+                                   (const bf16*)vcache, block_table, max_blocks, req_index, positions, nq, nkv, page_size, num_pages,
                                    scale * 1.4426950408889634f, window, chunk, S, part_acc, part_ml, err, token_index,
                                    (bf16*)out, arrivals, in_cluster, fz);
 }
@@ -922,9 +1028,11 @@ extern "C" int vl_flash_decode(const void* q, int q_stride, const void* kcache, 
                                const int* block_table, int max_blocks, const int* req_index, const int* positions,
                                int T, int nq, int nkv, int hd, int page_size, int num_pages, float scale, int window,
                                int chunk, int S, float* part_acc, float* part_ml, unsigned* err,
-                               const int* token_index, void* out, int* arrivals, const float* sinks, void* stream) {
+                               const int* token_index, void* out, int* arrivals, const float* sinks, int weighting,
+                               int block, const float* head_bias, const void* gate, int gate_stride, void* stream) {
     DecodeFusion fz = {};
     fz.sinks = sinks;
+    fz.op = AttnOptions{weighting, block, head_bias, (const bf16*)gate, gate_stride};
     return launch_flash_decode(q, q_stride, kcache, vcache, block_table, max_blocks, req_index, positions, T, nq, nkv, hd,
                                page_size, num_pages, scale, window, chunk, S, part_acc, part_ml, err, token_index, out,
                                arrivals, fz, stream);

@@ -55,12 +55,14 @@ _SIGNATURES = {
     ("attention", "vl_decode_attention_merge"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                                  c_int, c_int, c_void_p, c_void_p, c_void_p],
     ("flash_attn", "vl_flash_prefill"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                                         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p],
+                                         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
+                                         c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
     ("flash_tc5", "vl_flash_prefill_tc5"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                             c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p],
     ("flash_attn", "vl_flash_decode"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
-                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
     ("flash_attn", "vl_flash_decode_fused"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                               c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
                                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -474,19 +476,22 @@ def _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, h
 
 
 def flash_prefill(qkv, out, k_cache, v_cache, block_table, tiles, num_heads, num_kv_heads, head_dim, scale, window, err,
-                  tile_rows=64, sinks=None):
+                  tile_rows=64, sinks=None, weighting="softmax", mask_chunk=None, head_bias=None, gate=None):
     """Tensor-core (mma.sync) attention for prompt portions.  `tiles` int32 [n, 4]: (row of the block
     table, index of the tile's first token in the step, tokens (<= tile_rows), position of the first
-    token); the tiles of a step cover every token that the kernel is to serve once."""
+    token); the tiles of a step cover every token that the kernel is to serve once.
+    `weighting`, `mask_chunk` (the `chunk` there), `head_bias`, `gate`: see `_check_variant`."""
     _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, head_dim)
     _check_sinks(sinks, num_heads)
+    mode, mask_chunk, gate_stride = _check_variant(qkv, num_heads, weighting, mask_chunk, head_bias, gate, sinks)
     _need(out, torch.bfloat16, "out", 2); _need(tiles, torch.int32, "tiles", 2)
     if out.shape != (qkv.shape[0], num_heads * head_dim) or tiles.shape[1] != 4:
         raise KernelError("flash_prefill: shapes disagree")
     _check(_fn("flash_attn", "vl_flash_prefill", {"FA_HD": head_dim})(
         _ptr(qkv), qkv.shape[1], _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
         _ptr(tiles), tiles.shape[0], int(tile_rows), num_heads, num_kv_heads, head_dim, k_cache.shape[2],
-        k_cache.shape[0], float(scale), int(window or 0), _ptr(err), _ptr(sinks), _stream()), "vl_flash_prefill")
+        k_cache.shape[0], float(scale), int(window or 0), _ptr(err), _ptr(sinks), mode, mask_chunk, _ptr(head_bias),
+        _ptr(gate), gate_stride, _stream()), "vl_flash_prefill")
     return out
 
 
@@ -529,6 +534,9 @@ def _own_merge_cap(head_dim) -> int:
     return cap
 
 
+flash_decode_own_merge_cap = _own_merge_cap
+
+
 def flash_decode_arrivals(num_tokens, num_heads, num_kv_heads) -> int:
     """Counters (int32) that `flash_decode` needs in `arrivals` for this many tokens."""
     return num_tokens * num_kv_heads * -(-(num_heads // num_kv_heads) // 16)
@@ -549,7 +557,8 @@ def flash_decode_streams(dtype, num_tokens, num_kv_heads, head_dim, page_size, m
 
 def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, num_heads, num_kv_heads,
                  head_dim, scale, window, max_context, part_acc, part_ml, err, chunk=DECODE_CHUNK, token_index=None,
-                 stream_kernel=None, arrivals=None, fold=None, sinks=None):
+                 stream_kernel=None, arrivals=None, fold=None, sinks=None, weighting="softmax", mask_chunk=None,
+                 head_bias=None, gate=None):
     """Tensor-core version of `decode_attention` (bfloat16): every block takes a chunk of a token's
     keys; the chunks are merged by the block that finishes last (`arrivals`: int32 counters,
     `flash_decode_arrivals` of them, zero before the first call and left zero) or, without
@@ -562,9 +571,15 @@ def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, 
     `fold` = (q_weight, k_weight, eps, inv_freq, rotary_dim, slots) folds the step's `qk_norm_rope_write`
     into the block-per-chunk kernel (the TMA kernel does not take it): qkv then holds the rows as the
     projection left them, every token is the last of its request, and the token's key and value are
-    written to the cache by this launch (slots None: not written).  The same bits as the two kernels in turn."""
+    written to the cache by this launch (slots None: not written).  The same bits as the two kernels in turn.
+    `weighting`, `mask_chunk` (the `chunk` there), `head_bias`, `gate`: see `_check_variant`.  The sigmoid and the gate
+    go with the block-per-chunk kernel that merges its chunks itself (`arrivals` given, few enough chunks)."""
     _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, head_dim)
     _check_sinks(sinks, num_heads)
+    mode, mask_chunk, gate_stride = _check_variant(qkv, num_heads, weighting, mask_chunk, head_bias, gate, sinks)
+    variant = bool(mode or mask_chunk or gate is not None)
+    if variant and fold is not None:
+        raise KernelError("flash_decode: the folded head work goes with the plain softmax")
     if sinks is not None and fold is not None:
         raise KernelError("flash_decode: the folded head work and sinks do not go together")
     _need(out, torch.bfloat16, "out", 2)
@@ -579,6 +594,10 @@ def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, 
     S, need_acc, need_ml = decode_attention_scratch(T, num_heads, head_dim, max_context, chunk)
     if part_acc.numel() < need_acc or part_ml.numel() < need_ml:
         raise KernelError(f"flash_decode: scratch too small ({part_acc.numel()} < {need_acc})")
+    if variant:
+        if stream_kernel or arrivals is None or S > _own_merge_cap(head_dim):
+            raise KernelError("flash_decode: weighting, mask chunk and gate go with the kernel that merges its chunks itself")
+        stream_kernel = False
     if stream_kernel is None:
         stream_kernel = fold is None and flash_decode_streams(qkv.dtype, T, num_kv_heads, head_dim, k_cache.shape[2], max_context)
     if fold is not None and (stream_kernel or token_index is not None):
@@ -597,7 +616,8 @@ def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, 
                 raise KernelError("flash_decode: too few arrival counters")
         if fold is None:
             _check(_fn("flash_attn", "vl_flash_decode", {"FA_HD": head_dim})(
-                *args, _ptr(out) if arrivals is not None else None, _ptr(arrivals), _ptr(sinks), _stream()), "vl_flash_decode")
+                *args, _ptr(out) if arrivals is not None else None, _ptr(arrivals), _ptr(sinks), mode, mask_chunk,
+                _ptr(head_bias), _ptr(gate), gate_stride, _stream()), "vl_flash_decode")
         else:
             qw, kw, eps, inv_freq, rot, slots = fold
             for t, n in ((qw, "q_weight"), (kw, "k_weight"), (inv_freq, "inv_freq")):

@@ -36,9 +36,13 @@ def folds_head_work(dtype, step, spec, group, num_tokens) -> bool:
     return -(-int(group.max_context) // chunk) <= FOLD_MAX_CHUNKS
 
 
-def _decode(ops, args, step, spec, group, num_tokens, max_context, token_index=None, fold=None, sinks=None):
+def _decode(ops, args, step, spec, group, num_tokens, max_context, token_index=None, fold=None, sinks=None, variant=None):
     chunk = ops.decode_chunk_for(num_tokens, spec.num_kv_heads, max_context, head_dim=spec.head_dim)
     own_merge = True
+    if variant is not None:
+        # the keys a token reads end at its block of the mask: chunks as short as serve that reach, merged inside the launch
+        reach = min(int(max_context), int(variant["mask_chunk"] or max_context), int(spec.window or max_context))
+        chunk = min(chunk, 256 if reach <= 1024 else (512 if reach <= 2048 else 1024))
     if getattr(spec, "shared_row", False) and spec.num_heads >= 16:
         # One shared row for 16 heads and more (latent attention): the step is bound by the blocks' own pace, not by
         # bytes, and runs best with about four chunks over the keys a token reads, merged by the merge kernel
@@ -54,7 +58,15 @@ def _decode(ops, args, step, spec, group, num_tokens, max_context, token_index=N
     arrivals = step.workspace.zeros(step.tag + "attn.arrivals", ops.flash_decode_arrivals(num_tokens, spec.num_heads, spec.num_kv_heads),
                                     torch.int32) if own_merge else None
     return ops.flash_decode(*args, max_context, part_acc, part_ml, step.err, chunk=chunk, token_index=token_index,
-                            arrivals=arrivals, fold=fold, sinks=sinks)
+                            arrivals=arrivals, fold=fold, sinks=sinks, **(variant or {}))
+
+
+def _variant_decode_ok(ops, spec, num_tokens, max_context, mask_chunk) -> bool:
+    """Whether the block-per-chunk kernel can merge the chunks of this step itself, which its options ask for."""
+    chunk = ops.decode_chunk_for(num_tokens, spec.num_kv_heads, max_context, head_dim=spec.head_dim)
+    reach = min(int(max_context), int(mask_chunk or max_context), int(spec.window or max_context))
+    chunk = min(chunk, 256 if reach <= 1024 else (512 if reach <= 2048 else 1024))
+    return -(-int(max_context) // chunk) <= ops.flash_decode_own_merge_cap(spec.head_dim)
 
 
 def run(qkv, out, cache, group, step, spec, scale, fold=None, sinks=None, weighting="softmax", chunk=None,
@@ -91,7 +103,24 @@ def run(qkv, out, cache, group, step, spec, scale, fold=None, sinks=None, weight
 
 
 def _run_variant(ops, q, out, cache, group, step, spec, scale, weighting, chunk, head_bias, gate, sinks):
-    """Attention with another weighting than the softmax, a chunked mask or an output gate."""
+    """Attention with another weighting than the softmax, a chunked mask or an output gate: in bfloat16 the mma.sync
+    kernels for portions of prompts and the block-per-chunk kernel for single tokens, each with these options; in
+    float32, or where those do not take the head size or the step, the one kernel whose sums depend on positions alone."""
+    variant = dict(weighting=weighting, mask_chunk=chunk, head_bias=head_bias, gate=gate)
+    args = (q, out, cache.k, cache.v, group.block_table, step.req_index, step.positions,
+            spec.num_heads, spec.num_kv_heads, spec.head_dim, scale, spec.window)
+    if ops.flash_supported(q.dtype, spec.head_dim):
+        if step.max_query_len == 1:
+            if _variant_decode_ok(ops, spec, q.shape[0], group.max_context, chunk):
+                return _decode(ops, args, step, spec, group, q.shape[0], group.max_context, sinks=sinks, variant=variant)
+        elif step.query_tiles is not None and (step.single_tokens is None or _variant_decode_ok(
+                ops, spec, step.single_tokens.shape[0], step.single_context, chunk)):
+            ops.flash_prefill(q, out, cache.k, cache.v, group.block_table, step.query_tiles, spec.num_heads, spec.num_kv_heads,
+                              spec.head_dim, scale, spec.window, step.err, tile_rows=QUERY_TILE, sinks=sinks, **variant)
+            if step.single_tokens is not None:
+                _decode(ops, args, step, spec, group, step.single_tokens.shape[0], step.single_context,
+                        token_index=step.single_tokens, sinks=sinks, variant=variant)
+            return out
     return ops.paged_attention(q, out, cache.k, cache.v, group.block_table, step.req_index, step.positions,
                                spec.num_heads, spec.num_kv_heads, spec.head_dim, scale, spec.window, step.err, sinks=sinks,
                                weighting=weighting, chunk=chunk, head_bias=head_bias, gate=gate)
