@@ -524,6 +524,16 @@ def kikepel_bench(args):
         res["kernels_decode_b64"] = timed_step(runner, [StepEntry(rid, [i], [0]) for i, rid in enumerate(ids)])
         for rid in ids:
             runner.release(rid)
+        if name == "qwen3":
+            # the same step with as many keys a token as the other design's mask leaves it: attention at equal reads
+            reach = (context - 1) % block + 1
+            for rid in ids:
+                runner.cache.admit(rid)
+                runner.cache.append(rid, reach - 1)
+            runner.storage.zero_slots(runner.cache.take_fresh_slots())
+            res["kernels_decode_b64_equal_keys"] = timed_step(runner, [StepEntry(rid, [i], [0]) for i, rid in enumerate(ids)])
+            for rid in ids:
+                runner.release(rid)
         runner.check_device_errors()
         res["weights_GB"] = round(sum(p.numel() * p.element_size() for p in _tensors_of(runner.model)) / 1e9, 2)
         results[name] = res
@@ -636,6 +646,16 @@ def tuzisun_bench(args):
         res["kernels_decode_b64"] = timed_step(runner, [StepEntry(rid, [i], [0]) for i, rid in enumerate(ids)])
         for rid in ids:
             runner.release(rid)
+        if name == "qwen3":
+            # the same step with as many keys a token as the other design's mask leaves it: attention at equal reads
+            reach = (context - 1) % block + 1
+            for rid in ids:
+                runner.cache.admit(rid)
+                runner.cache.append(rid, reach - 1)
+            runner.storage.zero_slots(runner.cache.take_fresh_slots())
+            res["kernels_decode_b64_equal_keys"] = timed_step(runner, [StepEntry(rid, [i], [0]) for i, rid in enumerate(ids)])
+            for rid in ids:
+                runner.release(rid)
         runner.check_device_errors()
         res["weights_GB"] = round(sum(p.numel() * p.element_size() for p in _tensors_of(runner.model)) / 1e9, 2)
         results[name] = res
@@ -742,6 +762,16 @@ def sodonex_bench(args):
         res["kernels_decode_b64"] = timed_step(runner, [StepEntry(rid, [i], [0]) for i, rid in enumerate(ids)])
         for rid in ids:
             runner.release(rid)
+        if name == "qwen3":
+            # the same step with as many keys a token as the other design's mask leaves it: attention at equal reads
+            reach = (context - 1) % block + 1
+            for rid in ids:
+                runner.cache.admit(rid)
+                runner.cache.append(rid, reach - 1)
+            runner.storage.zero_slots(runner.cache.take_fresh_slots())
+            res["kernels_decode_b64_equal_keys"] = timed_step(runner, [StepEntry(rid, [i], [0]) for i, rid in enumerate(ids)])
+            for rid in ids:
+                runner.release(rid)
         runner.check_device_errors()
         res["weights_GB"] = round(sum(p.numel() * p.element_size() for p in _tensors_of(runner.model)) / 1e9, 2)
         results[name] = res
@@ -768,8 +798,10 @@ def sodonex_bench(args):
     roof["attention_decode_gbs"] = {
         "sodonex": gb(layers * B * reach * 2.0 * KV * D * 2.0, us(sx, "kernels_decode_b64", att)),
         "qwen3": gb(layers * B * context * 2.0 * KV * D * 2.0, us(q, "kernels_decode_b64", att)),
-        "keys_a_token": {"sodonex": reach, "qwen3": context},
-        "us_a_layer": {"sodonex": round(us(sx, "kernels_decode_b64", att) / layers, 1), "qwen3": round(us(q, "kernels_decode_b64", att) / layers, 1)}}
+        "qwen3_at_equal_keys": gb(layers * B * reach * 2.0 * KV * D * 2.0, us(q, "kernels_decode_b64_equal_keys", att)),
+        "keys_a_token": {"sodonex": reach, "qwen3": context, "qwen3_at_equal_keys": reach},
+        "us_a_layer": {"sodonex": round(us(sx, "kernels_decode_b64", att) / layers, 1), "qwen3": round(us(q, "kernels_decode_b64", att) / layers, 1),
+                       "qwen3_at_equal_keys": round(us(q, "kernels_decode_b64_equal_keys", att) / layers, 1)}}
     C = (H + KV) * D
     for step, rows in (("kernels_prefill", T), ("kernels_decode_b64", B)):
         r = {}

@@ -59,7 +59,7 @@ CONFIGS = {
                 layer(mixer(1, 1, 48, 5, 0.15, 100, 16, 1234.0), moe(32, 8, 3)),
                 layer(mixer(4, 1, 16, 3, 0.3, 4096, 2, 9.0), None)]),
     "C": model(301, 128, 1e-6, 11.0, 0.5,
-               [layer(mixer(8, 2, 64, 4, 0.125, 70, 32, 250000.0), moe(64, 8, 2)),
+               [layer(mixer(8, 2, 64, 4, 0.11, 70, 32, 300000.0), moe(64, 8, 2)),
                 layer(mixer(4, 4, 64, 2, 0.1, 64, 64, 10000.0), moe(96, 4, 3)),
                 layer(mixer(2, 1, 128, 4, 0.09, 128, 64, 1e6), None)]),
     "D": model(97, 72, 2e-5, 0.5, 1.3,
@@ -343,45 +343,51 @@ def in_portions(n, fn):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("W", [5, 64, 300])
-def test_token_shift_keeps_the_row_before(dtype, W):
+@pytest.mark.parametrize("pad", [3, 4])
+@pytest.mark.parametrize("W", [5, 64, 300, 2048])
+def test_token_shift_keeps_the_row_before(dtype, W, pad):
     """Two requests in portions, in swapped state rows of which one holds leftovers of an earlier request until it is
-    cleared: every mixed row equals the whole sequence's, and a first token is mixed with zeros."""
+    cleared: every mixed row equals the whole sequence's, and a first token is mixed with zeros.  `pad` floats lie
+    before the row in the state: with 4 of them the rows start on 16 bytes (the kernel's wide accesses), with 3 not."""
     n = [13, 6]
     x = [rand((n[b], W), 50 + b, scale=2.0) for b in (0, 1)]
     mu = rand((W,), 52, scale=0.5) + 0.5
     want = [P.token_shift(x[b].double().cpu(), mu.cpu()) for b in (0, 1)]
-    state = torch.zeros((2, 3 + W), device=DEV)
+    state = torch.zeros((2, pad + W), device=DEV)
 
     def step(live, lens, starts):
         s = mini_step(lens, [1 - b for b in live], starts)
         xin = torch.cat([x[b][a:a + c] for b, a, c in zip(live, starts, lens)]).contiguous()
         out = torch.empty((xin.shape[0], W), dtype=dtype, device=DEV)
-        ops().token_shift(xin, mu, state, 3, s.cu_seqlens, s.state_slots, s.req_index, s.positions, out)
+        ops().token_shift(xin, mu, state, pad, s.cu_seqlens, s.state_slots, s.req_index, s.positions, out)
         return out.float()
 
     got = in_portions(n, step)
     for b in (0, 1):
         close(got[b], want[b], dtype, "token shift", tol=1e-6 if dtype == torch.float32 else 8e-3)
-        assert torch.equal(state[1 - b, 3:], x[b][-1])                      # the last row a request brought
-    assert float(state[:, :3].abs().max()) == 0.0
+        assert torch.equal(state[1 - b, pad:], x[b][-1])                      # the last row a request brought
+    assert float(state[:, :pad].abs().max()) == 0.0
     close(got[0][0], (x[0][0].double() * (1 - mu.double())).cpu(), dtype, "a first token", tol=1e-6 if dtype == torch.float32 else 8e-3)
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("in_bias", [False, True])
 @pytest.mark.parametrize("taps,C", [(1, 5), (2, 40), (4, 33), (6, 128)])
-def test_convolution_without_bias_or_activation(taps, C):
+def test_convolution_without_bias_or_activation(taps, C, in_bias):
+    """`in_bias`: the bias of the product that made the rows, added by the kernel as it reads them (zeros before a
+    sequence's start stay zeros, the state keeps the rows with it)."""
     n = [13, 6]
     x = [rand((n[b], C + 3), 40 + b) for b in (0, 1)]
     w = rand((C, taps), 42)
-    want = [P.short_conv(x[b][:, 2:2 + C].double().cpu(), w.cpu()) for b in (0, 1)]
+    ib = rand((C,), 43) if in_bias else None
+    want = [P.short_conv(x[b][:, 2:2 + C].double().cpu() + (ib.double().cpu() if in_bias else 0.0), w.cpu()) for b in (0, 1)]
     state = torch.zeros((2, 7 + max((taps - 1) * C, 1)), device=DEV)
 
     def step(live, lens, starts):
         s = mini_step(lens, [1 - b for b in live], starts)
         xin = torch.cat([x[b][a:a + c] for b, a, c in zip(live, starts, lens)]).contiguous()
         out = torch.empty((xin.shape[0], C), device=DEV)
-        ops().short_conv(xin, 2, C, w, None, state, 7, s.cu_seqlens, s.state_slots, out, act=False)
+        ops().short_conv(xin, 2, C, w, None, state, 7, s.cu_seqlens, s.state_slots, out, act=False, in_bias=ib)
         return out
 
     got = in_portions(n, step)
@@ -393,7 +399,7 @@ def test_convolution_without_bias_or_activation(taps, C):
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H_,G_,D_,rot,base", [(4, 2, 16, 8, 10000.0), (2, 1, 24, 24, 500.0), (3, 3, 20, 6, 50.0),
-                                               (8, 2, 64, 32, 250000.0), (1, 1, 128, 2, 7.0)])
+                                               (8, 2, 64, 32, 200000.0), (1, 1, 128, 2, 7.0)])
 def test_whole_row_norm_rotation_and_cache_rows(dtype, H_, G_, D_, rot, base):
     """q and k are normed over the WHOLE row (a norm per head would be far off: the heads are given unequal sizes), the
     first `rot` features of every head turn by the position, the values are the keys as they came, and padded features
@@ -429,6 +435,54 @@ def test_whole_row_norm_rotation_and_cache_rows(dtype, H_, G_, D_, rot, base):
     if H_ > 1:
         per_head = P.unit_rms(q64.view(T, H_, D_), eps).reshape(T, -1) * qw.double().cpu()
         assert float((per_head - P.whole_row_norm(q64, qw.cpu(), eps)).abs().max()) > 0.3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H_,G_,D_,rot,taps", [(4, 2, 16, 8, 3), (2, 1, 24, 24, 1), (3, 3, 20, 6, 6), (8, 2, 64, 32, 4), (1, 1, 128, 2, 2)])
+def test_convolution_folded_into_the_row_kernel(dtype, H_, G_, D_, rot, taps):
+    """The convolution, the whole-row norms, the rotation and the cache rows in one launch against the two kernels in
+    turn, bit for bit: two requests in portions and single tokens (the launch renews the state itself when every request
+    brings one token), in swapped state rows; queries, cache rows and the states after every step."""
+    n, page, eps = [13, 6], 8, 1e-5
+    Dp = -(-D_ // 16) * 16
+    C = (H_ + G_) * D_
+    x = [rand((n[b], C + H_ + 3), 140 + b, dtype) for b in (0, 1)]
+    w, ib = rand((C, taps), 142), rand((C,), 143)
+    qw, kw = rand((H_ * D_,), 144) + 1.5, rand((G_ * D_,), 145) + 1.5
+    inv = torch.tensor([77.0 ** (-2.0 * i / rot) for i in range(rot // 2)], device=DEV)
+    width = 5 + max((taps - 1) * C, 1)
+    states = [torch.zeros((2, width), device=DEV) for _ in (0, 1)]
+    caches = [[torch.zeros((6, G_, page, Dp), dtype=dtype, device=DEV) for _ in (0, 1)] for _ in (0, 1)]
+    base = [0, 24]                                                          # cache slots of the two requests
+
+    def step(live, lens, starts):
+        s = mini_step(lens, [1 - b for b in live], starts)
+        xin = torch.cat([x[b][a:a + c] for b, a, c in zip(live, starts, lens)]).contiguous()
+        slots = ints([base[b] + a + i for b, a, c in zip(live, starts, lens) for i in range(c)])
+        T = xin.shape[0]
+        outs = []
+        for fused in (0, 1):
+            q = torch.empty((T, H_ * Dp), dtype=dtype, device=DEV)
+            kc, vc = caches[fused]
+            if fused:
+                ops().conv_rows_norm_rope_write(xin, w, ib, states[1], 5, s.cu_seqlens, s.state_slots, s.req_index, max(lens),
+                                                s.positions, slots, qw, kw, eps, inv, rot, q, kc, vc, H_, G_, D_, s.err,
+                                                padded_head_dim=Dp)
+            else:
+                qk = torch.empty((T, C), device=DEV)
+                ops().short_conv(xin, 0, C, w, None, states[0], 5, s.cu_seqlens, s.state_slots, qk, act=False, longest=max(lens),
+                                 in_bias=ib)
+                ops().rows_norm_rope_write(qk, s.positions, slots, qw, kw, eps, inv, rot, q, kc, vc, H_, G_, D_, s.err,
+                                           padded_head_dim=Dp)
+            outs.append(q)
+        assert int(s.err.item()) == 0
+        assert torch.equal(outs[0], outs[1]) and torch.equal(states[0], states[1])
+        return outs[1]
+
+    in_portions(n, step)
+    assert torch.equal(caches[0][0], caches[1][0]) and torch.equal(caches[0][1], caches[1][1])
+    assert float(caches[1][0].abs().max()) > 0 and float(states[1][:, :5].abs().max()) == 0.0
 
 
 def paged(seqs, page, G_, Dp, dtype, seed):
@@ -528,6 +582,72 @@ def test_tensor_core_kernels_take_the_weighting_the_blocks_and_the_gate(weightin
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("weighting", ["sigmoid", "softmax"])
+@pytest.mark.parametrize("H_,G_,D_,page,size", [(4, 2, 64, 16, 70), (2, 1, 128, 64, 64), (2, 2, 128, 16, 300), (8, 2, 64, 32, 129),
+                                                (6, 3, 64, 8, 1), (2, 1, 128, 128, 4096)])
+def test_tcgen05_prompt_kernel_takes_the_weighting_the_blocks_and_the_gate(weighting, H_, G_, D_, page, size):
+    """The kernel of long prompt portions (tcgen05, heads of 64 and 128): a portion of 170 tokens behind 130 cached ones,
+    so that its tiles begin and end inside blocks of the mask, against the float32 kernel and the plain sums."""
+    dtype, sig = torch.bfloat16, weighting == "sigmoid"
+    if not ops().flash_tc5_supported(dtype, D_, page):
+        pytest.skip("page size not taken by this kernel")
+    n, c = 300, 170
+    scale = 0.6 * D_ ** -0.5
+    seqs = [(rand((n, G_, D_), 170, dtype).cpu(), rand((n, G_, D_), 173, dtype).cpu())]
+    kc, vc, table = paged(seqs, page, G_, D_, dtype, 5)
+    q = rand((c, H_ * D_), 176, dtype)
+    pb = (rand((H_,), 177) - 1.0) if sig else None
+    gate = rand((c, H_ + 3), 178, dtype, 2.0)
+    e = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ref = torch.empty((c, H_ * D_), dtype=dtype, device=DEV)
+    ops().paged_attention(q, ref, kc, vc, table, ints([0] * c), ints(range(n - c, n)), H_, G_, D_, scale, None, e,
+                          weighting=weighting, chunk=size, head_bias=pb, gate=gate[:, 1:])
+    tiles = torch.tensor([[0, 0, 128, 130], [0, 128, 42, 258]], dtype=torch.int32, device=DEV)
+    out = torch.full((c, H_ * D_), float("nan"), dtype=dtype, device=DEV)
+    ops().flash_prefill_tc5(q, out, kc, vc, table, tiles, H_, G_, D_, scale, None, e, weighting=weighting, mask_chunk=size,
+                            head_bias=pb, gate=gate[:, 1:])
+    assert int(e.item()) == 0
+    close(out, ref, dtype, "against the float32 kernel", tol=1.5e-2)
+    if sig:
+        k, v = (t.double() for t in seqs[0])
+        qfull = torch.zeros(n, H_, D_, dtype=torch.float64)
+        qfull[n - c:] = q.double().cpu().view(c, H_, D_)
+        want = P.sigmoid_chunk_weights(qfull, k, v, pb.cpu(), scale, size)[n - c:]
+        want = want * torch.sigmoid(gate[:, 1:1 + H_].double().cpu())[:, :, None]
+        close(out.view(c, H_, D_), want, dtype, "sigmoid attention on tcgen05", tol=1.5e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("size,far,seen", [(1024, 3, True), (512, 512, True), (512, 511, False), (300, 599, False), (300, 600, True),
+                                           (150, 600, True), (150, 599, False), (64, 576, True), (64, 575, False), (128, 512, True),
+                                           (128, 511, False)])
+def test_tcgen05_prompt_kernel_sees_one_far_key_inside_the_block_only(size, far, seen):
+    """As `test_one_far_key_among_hundreds`, for the kernel of long prompt portions: the query at position 600 is the
+    last row of a portion of 100 tokens; every weight is near zero but for the key at `far`, whose value is a marker."""
+    dtype, H_, G_, D_, page, n, T = torch.bfloat16, 2, 1, 64, 16, 601, 100
+    k = rand((n, G_, D_), 180, dtype, 0.1).cpu()
+    v = rand((n, G_, D_), 181, dtype, 0.1).cpu()
+    q = rand((1, H_ * D_), 182, dtype, 0.1)
+    k[far, 0] = 0.0
+    k[far, 0, 5] = 8.0
+    v[far, 0] = 100.0
+    q[0, 5], q[0, D_ + 5] = 4.0, 4.0
+    pb = torch.full((H_,), -12.0, device=DEV)
+    kc, vc, table = paged([(k, v)], page, G_, D_, dtype, 6)
+    qs = torch.cat([rand((T - 1, H_ * D_), 183, dtype, 0.1), q]).contiguous()
+    out = torch.empty((T, H_ * D_), dtype=dtype, device=DEV)
+    e = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops().flash_prefill_tc5(qs, out, kc, vc, table, ints([0, 0, T, n - T]).view(1, 4), H_, G_, D_, 1.0, None, e,
+                            weighting="sigmoid", mask_chunk=size, head_bias=pb)
+    assert int(e.item()) == 0
+    got = out[-1].float().cpu()
+    if seen:
+        assert float((got - 100.0).abs().max()) < 1.0, got[:4]
+    else:
+        assert float(got.abs().max()) < 0.1, got[:4]
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("size,far,seen", [(1024, 3, True), (1024, 0, True), (512, 512, True), (512, 511, False), (300, 599, False), (300, 600, True), (150, 600, True), (150, 599, False), (64, 576, True),
                                            (64, 575, False)])
@@ -576,8 +696,9 @@ def test_one_far_key_among_hundreds(dtype, size, far, seen):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("W,g,mult", [(64, 1.7, 0.7), (72, 1.0, 1.0), (320, 0.3, 0.5), (1000, -2.0, 1.3)])
-def test_norm_with_one_number_adds_into_the_stream(dtype, W, g, mult):
+@pytest.mark.parametrize("W,g,mult,bias", [(64, 1.7, 0.7, False), (72, 1.0, 1.0, True), (320, 0.3, 0.5, True), (1000, -2.0, 1.3, False),
+                                          (1002, 0.5, 0.25, True), (4096, 1.1, 0.5, True)])
+def test_norm_with_one_number_adds_into_the_stream(dtype, W, g, mult, bias):
     from vllm_lite_b200.parts import spec as S
     from vllm_lite_b200.parts.base import BuildContext
     from vllm_lite_b200.parts.registry import NORMS
@@ -586,10 +707,14 @@ def test_norm_with_one_number_adds_into_the_stream(dtype, W, g, mult):
     part = NORMS.get("rms_norm")(spec, {"": torch.tensor(g, dtype=dtype)}, BuildContext(torch.device(DEV), dtype))
     y = rand((T, W), 90, dtype, 0.02)                                       # small rows: eps counts inside the root
     x = rand((T, W), 91)
-    want = x.double().cpu() + mult * P.scalar_norm(y.double().cpu(), torch.tensor(g, dtype=dtype), eps)
+    vec = rand((W,), 92, scale=0.02) if bias else None                      # left to the norm's kernel by the product before
+    yb = y.double().cpu() + (vec.double().cpu() if bias else 0.0)
+    want = x.double().cpu() + mult * P.scalar_norm(yb, torch.tensor(g, dtype=dtype), eps)
     assert float((P.scalar_norm(y.double().cpu(), torch.tensor(g), 0.0) - P.scalar_norm(y.double().cpu(), torch.tensor(g), eps)).abs().max()) > 0.05
     cast = torch.empty((T, W), dtype=dtype, device=DEV) if dtype != torch.float32 else None
     kw = {} if mult == 1.0 else {"mult": mult}
+    if bias:
+        kw["bias"] = vec
     part.add_normed(y, x, mini_step([T], [0]), cast, **kw)
     close(x, want, torch.float32, "stream", tol=3e-6)
     if cast is not None:

@@ -155,3 +155,24 @@ static inline int vl_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
     cfg.numAttrs = vl_pdl_enabled() ? 1 : 0;
     return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
+
+// Four neighbouring values of a row as float32: one 16-byte (float32) or 8-byte (bfloat16) access.
+template <typename TA> struct Quad;
+template <> struct Quad<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Quad<bf16> {
+    static __device__ __forceinline__ float4 load(const bf16* p) {
+        const uint2 r = *reinterpret_cast<const uint2*>(p);
+        return make_float4(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xffff0000u),
+                           __uint_as_float(r.y << 16), __uint_as_float(r.y & 0xffff0000u));
+    }
+    static __device__ __forceinline__ void store(bf16* p, float4 v) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        uint2 r;
+        r.x = *reinterpret_cast<unsigned*>(&lo);
+        r.y = *reinterpret_cast<unsigned*>(&hi);
+        *reinterpret_cast<uint2*>(p) = r;
+    }
+};

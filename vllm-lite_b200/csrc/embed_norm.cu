@@ -60,26 +60,6 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__
 // The same function with a row kept in registers: 16-byte loads, one pass over memory.
 // Thread i holds the float4 pieces i, i + 256, ... of the row (H a multiple of 4, at most
 // 256 * 4 * VPT values).  The sum of squares is taken piece by piece in that fixed order.
-template <typename TA> struct Quad;
-template <> struct Quad<float> {
-    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
-    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
-};
-template <> struct Quad<bf16> {
-    static __device__ __forceinline__ float4 load(const bf16* p) {
-        const uint2 r = *reinterpret_cast<const uint2*>(p);
-        return make_float4(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xffff0000u),
-                           __uint_as_float(r.y << 16), __uint_as_float(r.y & 0xffff0000u));
-    }
-    static __device__ __forceinline__ void store(bf16* p, float4 v) {
-        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
-        uint2 r;
-        r.x = *reinterpret_cast<unsigned*>(&lo);
-        r.y = *reinterpret_cast<unsigned*>(&hi);
-        *reinterpret_cast<uint2*>(p) = r;
-    }
-};
-
 template <typename TA, int VPT>
 __global__ void __launch_bounds__(256)
 add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restrict__ delta, const int* __restrict__ rows,
@@ -283,23 +263,24 @@ extern "C" int vl_layernorm_rows(const float* x, const int* rows, const float* w
 
 // RMS norm of a sub-layer's OUTPUT added into the stream with a factor: x[r] += mult * (y[r] / sqrt(mean(y[r]^2) + eps) * w)
 // (y in the activation dtype, x the float32 stream, everything between in float32) and, when asked, cast[r] = x[r] in
-// the activation dtype: the next sub-layer's input.  The row of y is kept in registers where it fits (H a multiple of
+// the activation dtype: the next sub-layer's input.  `bias` (or null): a vector added to every row of y first, in float32
+// (the bias of the product that made y, left to this kernel).  The row of y is kept in registers where it fits (H a multiple of
 // 4, at most 256 * 4 * VPT values), else read twice.  The order of the sums depends on the row length alone.
 template <typename TA>
 __global__ void __launch_bounds__(256)
-rmsnorm_add_kernel(const TA* __restrict__ y, const float* __restrict__ w, float eps, float mult, float* __restrict__ x,
-                   TA* __restrict__ cast, int H) {
+rmsnorm_add_kernel(const TA* __restrict__ y, const float* __restrict__ bias, const float* __restrict__ w, float eps, float mult,
+                   float* __restrict__ x, TA* __restrict__ cast, int H) {
     __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
     const int r = blockIdx.x;
     const TA* yr = y + (size_t)r * H;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += 256) { const float d = to_f32(yr[i]); ss += d * d; }
+    for (int i = threadIdx.x; i < H; i += 256) { const float d = to_f32(yr[i]) + (bias ? bias[i] : 0.f); ss += d * d; }
     const float inv = 1.0f / sqrtf(block_sum<256>(ss, scratch) / (float)H + eps);
     float* xr = x + (size_t)r * H;
     for (int i = threadIdx.x; i < H; i += 256) {
-        const float v = xr[i] + mult * (to_f32(yr[i]) * inv * w[i]);
+        const float v = xr[i] + mult * ((to_f32(yr[i]) + (bias ? bias[i] : 0.f)) * inv * w[i]);
         xr[i] = v;
         if (cast) cast[(size_t)r * H + i] = from_f32<TA>(v);
     }
@@ -307,8 +288,8 @@ rmsnorm_add_kernel(const TA* __restrict__ y, const float* __restrict__ w, float 
 
 template <typename TA, int VPT>
 __global__ void __launch_bounds__(256)
-rmsnorm_add_vec_kernel(const TA* __restrict__ y, const float* __restrict__ w, float eps, float mult, float* __restrict__ x,
-                       TA* __restrict__ cast, int H) {
+rmsnorm_add_vec_kernel(const TA* __restrict__ y, const float* __restrict__ bias, const float* __restrict__ w, float eps, float mult,
+                       float* __restrict__ x, TA* __restrict__ cast, int H) {
     __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
@@ -321,6 +302,10 @@ rmsnorm_add_vec_kernel(const TA* __restrict__ y, const float* __restrict__ w, fl
         const int c = threadIdx.x + 256 * i;
         if (c < H4) {
             v[i] = Quad<TA>::load(yr + 4 * c);
+            if (bias) {
+                const float4 b = Quad<float>::load(bias + 4 * c);
+                v[i].x += b.x; v[i].y += b.y; v[i].z += b.z; v[i].w += b.w;
+            }
             ss += v[i].x * v[i].x; ss += v[i].y * v[i].y; ss += v[i].z * v[i].z; ss += v[i].w * v[i].w;
         }
     }
@@ -341,22 +326,22 @@ rmsnorm_add_vec_kernel(const TA* __restrict__ y, const float* __restrict__ w, fl
 }
 
 template <typename TA>
-static int launch_rmsnorm_add(const TA* y, const float* w, float eps, float mult, float* x, TA* cast, int R, int H, cudaStream_t s) {
+static int launch_rmsnorm_add(const TA* y, const float* bias, const float* w, float eps, float mult, float* x, TA* cast, int R, int H, cudaStream_t s) {
     const int pieces = (H / 4 + 255) / 256;
-    if (H % 4 == 0 && pieces <= 1) return vl_launch(rmsnorm_add_vec_kernel<TA, 1>, dim3(R), dim3(256), 0, s, y, w, eps, mult, x, cast, H);
-    if (H % 4 == 0 && pieces <= 2) return vl_launch(rmsnorm_add_vec_kernel<TA, 2>, dim3(R), dim3(256), 0, s, y, w, eps, mult, x, cast, H);
-    if (H % 4 == 0 && pieces <= 4) return vl_launch(rmsnorm_add_vec_kernel<TA, 4>, dim3(R), dim3(256), 0, s, y, w, eps, mult, x, cast, H);
-    if (H % 4 == 0 && pieces <= 8) return vl_launch(rmsnorm_add_vec_kernel<TA, 8>, dim3(R), dim3(256), 0, s, y, w, eps, mult, x, cast, H);
-    return vl_launch(rmsnorm_add_kernel<TA>, dim3(R), dim3(256), 0, s, y, w, eps, mult, x, cast, H);
+    if (H % 4 == 0 && pieces <= 1) return vl_launch(rmsnorm_add_vec_kernel<TA, 1>, dim3(R), dim3(256), 0, s, y, bias, w, eps, mult, x, cast, H);
+    if (H % 4 == 0 && pieces <= 2) return vl_launch(rmsnorm_add_vec_kernel<TA, 2>, dim3(R), dim3(256), 0, s, y, bias, w, eps, mult, x, cast, H);
+    if (H % 4 == 0 && pieces <= 4) return vl_launch(rmsnorm_add_vec_kernel<TA, 4>, dim3(R), dim3(256), 0, s, y, bias, w, eps, mult, x, cast, H);
+    if (H % 4 == 0 && pieces <= 8) return vl_launch(rmsnorm_add_vec_kernel<TA, 8>, dim3(R), dim3(256), 0, s, y, bias, w, eps, mult, x, cast, H);
+    return vl_launch(rmsnorm_add_kernel<TA>, dim3(R), dim3(256), 0, s, y, bias, w, eps, mult, x, cast, H);
 }
 
-extern "C" int vl_rmsnorm_add(const void* y, int act_dtype, const float* w, float eps, float mult, float* x, void* cast,
+extern "C" int vl_rmsnorm_add(const void* y, int act_dtype, const float* bias, const float* w, float eps, float mult, float* x, void* cast,
                               int R, int H, void* stream) {
     if (R <= 0) return VL_OK;
     if (H <= 0) return VL_ERR_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
-    if (act_dtype == VL_F32) return launch_rmsnorm_add<float>((const float*)y, w, eps, mult, x, (float*)cast, R, H, s);
-    if (act_dtype == VL_BF16) return launch_rmsnorm_add<bf16>((const bf16*)y, w, eps, mult, x, (bf16*)cast, R, H, s);
+    if (act_dtype == VL_F32) return launch_rmsnorm_add<float>((const float*)y, bias, w, eps, mult, x, (float*)cast, R, H, s);
+    if (act_dtype == VL_BF16) return launch_rmsnorm_add<bf16>((const bf16*)y, bias, w, eps, mult, x, (bf16*)cast, R, H, s);
     return VL_ERR_UNSUPPORTED;
 }
 

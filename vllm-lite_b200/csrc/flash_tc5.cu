@@ -31,6 +31,10 @@
 // A row keeps a stale maximum until the true one exceeds it by more than 8 (in log2 units): the
 // probabilities then reach 2^8 at most, and output and sum are scaled alike, so the quotient is the
 // same; the decision is taken row by row, so a row's result does not depend on its neighbours.
+// Options of a launch (the same numbers as csrc/attention.cu and csrc/flash_attn.cu): `mask_block` > 0 cuts the positions
+// into blocks of that many, counted from position 0, and a query reads no key of an earlier block; with SIG (the kernel's
+// template argument) a visible key weighs sigmoid(s_j + head_bias[h]) by itself: no maximum, no sum, no rescaling, and
+// nothing is divided; `gate` multiplies head h's output for token t by sigmoid(gate[t * gate_stride + h]).
 // Every wait on an mbarrier is bounded; when one expires the block records VL_DEV_WAIT_EXPIRED,
 // stops, and still frees its TMEM.
 #include "tc5.cuh"
@@ -59,6 +63,13 @@ constexpr float RESCALE_ABOVE = 8.0f;
 __device__ __forceinline__ float exp2_mufu(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// 1 / (1 + 2^(-x)) for x in units of log2 (x = -inf gives 0, x = +inf gives 1)
+__device__ __forceinline__ float sigmoid_log2(float x) {
+    float e, y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-x));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(1.f + e));
     return y;
 }
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
@@ -106,13 +117,15 @@ __device__ __forceinline__ unsigned swizzled(int row, int chunk) {
 
 // tiles[i] = {row of the block table, index of the tile's first token in the step, tokens (<= 128),
 // position of the first}
-extern "C" __global__ void __launch_bounds__(NTHREADS, 2)
+template <bool SIG>
+__global__ void __launch_bounds__(NTHREADS, 2)
 flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                  const __grid_constant__ CUtensorMap pages_k, const __grid_constant__ CUtensorMap pages_v, int use_pages,
                  const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                  const int* __restrict__ block_table, int max_blocks, const int4* __restrict__ tiles, int num_tiles,
                  int nq, int nkv, int page_size, int num_pages, float scale_log2, int window, unsigned* err,
-                 const float* __restrict__ sinks) {
+                 const float* __restrict__ sinks, int mask_block, const float* __restrict__ head_bias,
+                 const bf16* __restrict__ gate, int gate_stride) {
     // tiles of the 128-byte swizzle must start on 1024-byte boundaries; there is no static shared
     // memory in this kernel, so the array starts the block's window
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -162,7 +175,8 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     const int req = tile.x, tok0 = tile.y, count = tile.z, pos0 = tile.w;
     const int h = blockIdx.x, kvh = h / (nq / nkv);
     const int hi = pos0 + count - 1;                             // the last key any row reads
-    const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;   // the first key any row reads
+    int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;         // the first key any row reads
+    if (mask_block > 0) lo = max(lo, pos0 / mask_block * mask_block);
     const int jt0 = lo / BN, n_tiles = hi / BN - jt0 + 1;
 
     // the query tile, rows beyond `count` zero, into the swizzled layout
@@ -302,7 +316,14 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     } else {                                                     // ---- softmax: a thread per query row ----
         const int row = warp * 32 + lane;
         const int qpos = pos0 + row;
-        const int first_key = (window > 0 && qpos - window + 1 > 0) ? qpos - window + 1 : 0;
+        int first_key = (window > 0 && qpos - window + 1 > 0) ? qpos - window + 1 : 0;
+        if (mask_block > 0) first_key = max(first_key, qpos / mask_block * mask_block);
+        // the first key that the last row of this warp reads (its window, its block of the mask): a tile that begins
+        // earlier holds keys that some row must not read
+        int warp_first = window > 0 ? pos0 + warp * 32 + 31 - window + 1 : 0;
+        if (mask_block > 0) warp_first = max(warp_first, (pos0 + warp * 32 + 31) / mask_block * mask_block);
+        const float bias_log2 = (SIG && head_bias) ? head_bias[h] * 1.4426950408889634f : 0.f;
+        const unsigned masked = (SIG && scale_log2 < 0.f) ? 0x7f800000u : 0xff800000u;   // times the scale: -inf
         const unsigned lane_base = (unsigned)(warp * 32) << 16;
         float m = -INFINITY, l = 0.f;
         bool ok = true;
@@ -318,39 +339,48 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             mbar_arrive(&s_free[s]);                             // the scores are in registers: the buffer may be written again
             const int j0 = (jt0 + it) * BN;
             // (warp-uniform) does any row of this warp see a key of the tile that it must not read?
-            const bool edge = (j0 + BN - 1 > pos0 + warp * 32) || (window > 0 && j0 < pos0 + warp * 32 + 31 - window + 1);
+            const bool edge = (j0 + BN - 1 > pos0 + warp * 32) || j0 < warp_first;
             float mx = -INFINITY;
             if (edge) {
 #pragma unroll
                 for (int c = 0; c < BN; ++c)
-                    if (j0 + c > qpos || j0 + c < first_key) sv[c] = 0xff800000u;     // -inf
+                    if (j0 + c > qpos || j0 + c < first_key) sv[c] = masked;          // -inf
             }
-#pragma unroll
-            for (int c = 0; c < BN; c += 2) mx = max3(mx, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]));
-            const float m_new = fmaxf(m, mx * scale_log2);       // the scale is positive
-            const bool bump = (m_new - m) > RESCALE_ABOVE;       // false when both are -inf (NaN compares false)
-            const float corr = bump ? exp2_mufu(m - m_new) : 1.0f;
-            if (bump) m = m_new;
-            const float base = (m == -INFINITY) ? 0.f : m;
-            const unsigned long long scale2 = pair(scale_log2, scale_log2), nbase2 = pair(-base, -base);
             unsigned pk[BN / 2];
-            unsigned long long sum2 = pair(0.f, 0.f);
+            bool bump = false;
+            float corr = 1.0f;
+            if constexpr (SIG) {
 #pragma unroll
-            for (int c = 0; c < BN; c += 2) {
-                float t0, t1;
-                unpair(fma2(pair(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, nbase2), t0, t1);
-                const float p0 = exp2_mufu(t0), p1 = exp2_mufu(t1);
-                sum2 = add2(sum2, pair(p0, p1));
-                pk[c >> 1] = pack_bf16(p0, p1);
+                for (int c = 0; c < BN; c += 2)
+                    pk[c >> 1] = pack_bf16(sigmoid_log2(fmaf(__uint_as_float(sv[c]), scale_log2, bias_log2)),
+                                           sigmoid_log2(fmaf(__uint_as_float(sv[c + 1]), scale_log2, bias_log2)));
+            } else {
+#pragma unroll
+                for (int c = 0; c < BN; c += 2) mx = max3(mx, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]));
+                const float m_new = fmaxf(m, mx * scale_log2);       // the scale is positive
+                bump = (m_new - m) > RESCALE_ABOVE;                  // false when both are -inf (NaN compares false)
+                corr = bump ? exp2_mufu(m - m_new) : 1.0f;
+                if (bump) m = m_new;
+                const float base = (m == -INFINITY) ? 0.f : m;
+                const unsigned long long scale2 = pair(scale_log2, scale_log2), nbase2 = pair(-base, -base);
+                unsigned long long sum2 = pair(0.f, 0.f);
+#pragma unroll
+                for (int c = 0; c < BN; c += 2) {
+                    float t0, t1;
+                    unpair(fma2(pair(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, nbase2), t0, t1);
+                    const float p0 = exp2_mufu(t0), p1 = exp2_mufu(t1);
+                    sum2 = add2(sum2, pair(p0, p1));
+                    pk[c >> 1] = pack_bf16(p0, p1);
+                }
+                float sum, sum_hi;
+                unpair(sum2, sum, sum_hi);
+                sum += sum_hi;
+                l = l * corr + sum;
             }
-            float sum, sum_hi;
-            unpair(sum2, sum, sum_hi);
-            sum += sum_hi;
-            l = l * corr + sum;
             if (it > 0) {                                        // P of the tile before has been read, O is at rest
                 if (!__all_sync(0xffffffffu, mbar_wait_bounded(&pv_done, (unsigned)((it - 1) & 1)))) { ok = false; break; }
                 tc5_fence_after();
-                if (__any_sync(0xffffffffu, bump)) {
+                if (!SIG && __any_sync(0xffffffffu, bump)) {
 #pragma unroll
                     for (int c0 = 0; c0 < HD; c0 += 32) {
                         unsigned ov[32];
@@ -371,8 +401,10 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
         }
         if (ok && __all_sync(0xffffffffu, mbar_wait_bounded(&pv_done, (unsigned)((n_tiles - 1) & 1)))) {
             tc5_fence_after();
-            float inv = l > 0.f ? 1.0f / l : 0.f;
-            if (sinks && m != -INFINITY) {
+            float inv = SIG ? 1.0f : (l > 0.f ? 1.0f / l : 0.f);
+            if (gate && row < count)
+                inv *= 1.f / (1.f + __expf(-__bfloat162float(gate[(size_t)(tok0 + row) * gate_stride + h])));
+            if (!SIG && sinks && m != -INFINITY) {
                 // a sink: one more term 2^sink (log2 units, not scaled) in the denominator.  l is a sum of terms
                 // relative to the base m, so with M = max(m, sink): 2^(m - M) / (l 2^(m - M) + 2^(sink - M))
                 const float sk = sinks[h] * 1.4426950408889634f, M = fmaxf(m, sk), a = exp2f(m - M);
@@ -413,9 +445,11 @@ extern "C" int vl_flash_tc5_head_dim() { return HD; }
 extern "C" int vl_flash_prefill_tc5(const void* q, int q_stride, void* out, const void* kcache, const void* vcache,
                                     const int* block_table, int max_blocks, const int* tiles, int num_tiles,
                                     int nq, int nkv, int hd, int page_size, int num_pages, float scale, int window,
-                                    unsigned* err, const float* sinks, void* stream) {
+                                    unsigned* err, const float* sinks, int weighting, int mask_block, const float* head_bias,
+                                    const void* gate, int gate_stride, void* stream) {
     if (num_tiles <= 0) return VL_OK;
     if (hd != HD) return VL_ERR_UNSUPPORTED;
+    if (weighting < 0 || weighting > 1 || mask_block < 0 || (gate && gate_stride < nq) || (weighting == 1 && sinks)) return VL_ERR_ARGUMENT;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || num_pages <= 0) return VL_ERR_ARGUMENT;
     if (page_size % 8 || (page_size < BN ? BN % page_size : page_size % BN)) return VL_ERR_UNSUPPORTED;
     if (q_stride % 8 || (((uintptr_t)q | (uintptr_t)out | (uintptr_t)kcache | (uintptr_t)vcache) & 15)) return VL_ERR_UNSUPPORTED;
@@ -437,9 +471,11 @@ extern "C" int vl_flash_prefill_tc5(const void* q, int q_stride, void* out, cons
         rc = tc5_make_map_pages(&pages_v, vcache, num_pages, nkv, page_size, HD, BN / page_size);
         if (rc) return rc;
     }
-    cudaError_t e = cudaFuncSetAttribute(flash_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    auto kernel = weighting == 1 ? flash_tc5_kernel<true> : flash_tc5_kernel<false>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
-    return vl_launch(flash_tc5_kernel, dim3(nq, num_tiles), dim3(NTHREADS), SMEM_BYTES, (cudaStream_t)stream,
+    return vl_launch(kernel, dim3(nq, num_tiles), dim3(NTHREADS), SMEM_BYTES, (cudaStream_t)stream,
                      map_k, map_v, pages_k, pages_v, use_pages, (const bf16*)q, q_stride, (bf16*)out, block_table, max_blocks, (const int4*)tiles,
-                     num_tiles, nq, nkv, page_size, num_pages, scale * 1.4426950408889634f, window, err, sinks);
+                     num_tiles, nq, nkv, page_size, num_pages, scale * 1.4426950408889634f, window, err, sinks, mask_block,
+                     head_bias, (const bf16*)gate, gate_stride);
 }

@@ -33,7 +33,7 @@ def dtype_code(dtype) -> int:
 
 _SIGNATURES = {
     ("embed_norm", "vl_embed"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
-    ("embed_norm", "vl_rmsnorm_add"): [c_void_p, c_int, c_void_p, c_float, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    ("embed_norm", "vl_rmsnorm_add"): [c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p],
     ("embed_norm", "vl_add_rmsnorm"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     ("embed_norm", "vl_add_bias"): [c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p],
     ("embed_norm", "vl_cast"): [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p],
@@ -43,6 +43,10 @@ _SIGNATURES = {
     ("attention", "vl_paged_attention"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                           c_float, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+    ("rope_cache", "vl_conv_rows_norm_rope_write"): [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p,
+                                                     c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
+                                                     c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                     c_int, c_int, c_int, c_longlong, c_void_p, c_void_p],
     ("rope_cache", "vl_rows_norm_rope_write"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int,
                                                 c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                                 c_longlong, c_void_p, c_void_p],
@@ -58,7 +62,8 @@ _SIGNATURES = {
                                          c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
                                          c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
     ("flash_tc5", "vl_flash_prefill_tc5"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                                            c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p],
+                                            c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
+                                            c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
     ("flash_attn", "vl_flash_decode"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
                                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -110,7 +115,7 @@ _SIGNATURES = {
     ("hyper", "vl_hc_step"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                               c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     ("hyper", "vl_dyt_rows"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-    ("recurrent", "vl_short_conv"): [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_longlong,
+    ("recurrent", "vl_short_conv"): [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong,
                                      c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p],
     ("recurrent", "vl_ssd_scan"): [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                    c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
@@ -304,6 +309,64 @@ def rows_norm_rope_write(qk, positions, slots, q_weight, k_weight, eps, inv_freq
         int(rotary_dim if inv_freq is not None else 0), _ptr(q_out), dtype_code(q_out.dtype),
         _ptr(k_cache) if slots is not None else None, _ptr(v_cache) if slots is not None else None, T, num_heads,
         num_kv_heads, head_dim, hdp, page_size, num_slots, _ptr(err), _stream()), "vl_rows_norm_rope_write")
+    return q_out
+
+
+_conv_rows_max = None
+
+
+def conv_rows_fused_ok(channels) -> bool:
+    """Whether `conv_rows_norm_rope_write` takes rows of this many q and k channels (it keeps one in shared memory)."""
+    global _conv_rows_max
+    if _conv_rows_max is None:
+        _conv_rows_max = int(build.load("rope_cache").vl_conv_rows_max())
+    return 0 < channels <= _conv_rows_max
+
+
+def conv_rows_norm_rope_write(proj, weight, in_bias, state, state_off, cu, state_slots, req_index, longest, positions, slots,
+                              q_weight, k_weight, eps, inv_freq, rotary_dim, q_out, k_cache, v_cache, num_heads, num_kv_heads,
+                              head_dim, err, padded_head_dim=None):
+    """`short_conv` (no activation, `in_bias` added to the rows as they are read) of the first (nq + nkv) hd columns of
+    proj [T, ld] and `rows_norm_rope_write` of the result in one launch: the convolved row stays in shared memory.  The
+    request's state row [(taps-1), C] at `state_off` is read by this launch and renewed by it when every request brings
+    one token (`longest` == 1), else by the convolution's state pass that follows.  The same bits as the two in turn."""
+    _need(proj, None, "proj", 2); _need(weight, torch.float32, "weight", 2); _need(positions, torch.int32, "positions", 1)
+    _need(q_weight, torch.float32, "q_weight", 1); _need(k_weight, torch.float32, "k_weight", 1); _need(q_out, proj.dtype, "q_out", 2)
+    _need(req_index, torch.int32, "req_index", 1)
+    T = proj.shape[0]
+    Cq, Ck = num_heads * head_dim, num_kv_heads * head_dim
+    C, taps = Cq + Ck, weight.shape[1]
+    hdp = int(padded_head_dim or head_dim)
+    if proj.shape[1] < C or weight.shape[0] != C or positions.shape[0] != T or req_index.shape[0] != T \
+            or q_out.shape != (T, num_heads * hdp) or q_weight.shape[0] != Cq or k_weight.shape[0] != Ck:
+        raise KernelError(f"conv_rows_norm_rope_write: proj {tuple(proj.shape)}, q_out {tuple(q_out.shape)}, heads {num_heads}+{num_kv_heads} x {head_dim}")
+    if in_bias is not None:
+        _need(in_bias, torch.float32, "in_bias", 1)
+        if in_bias.shape[0] != C:
+            raise KernelError("conv_rows_norm_rope_write: in_bias has one entry per channel")
+    page_size, num_slots = 1, 0
+    if slots is not None:
+        _need(slots, torch.int32, "slots", 1)
+        _need(k_cache, q_out.dtype, "k_cache", 4); _need(v_cache, q_out.dtype, "v_cache", 4)
+        if k_cache.shape != v_cache.shape or k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != hdp:
+            raise KernelError(f"cache {tuple(k_cache.shape)} does not match kv heads {num_kv_heads} x {hdp}")
+        page_size = k_cache.shape[2]
+        num_slots = k_cache.shape[0] * page_size
+    if inv_freq is not None:
+        _need(inv_freq, torch.float32, "inv_freq", 1)
+        if inv_freq.shape[0] * 2 != rotary_dim:
+            raise KernelError("inv_freq must have rotary_dim / 2 entries")
+    _seg_args(cu, state_slots)
+    sp, stride = _state_args(state, state_off, max((taps - 1) * C, 1))
+    longest = int(longest or max(T, 1))
+    _check(_fn("rope_cache", "vl_conv_rows_norm_rope_write")(
+        _ptr(proj), proj.shape[1], _ptr(weight), _ptr(in_bias), taps, sp, stride, _ptr(cu), _ptr(state_slots), _ptr(req_index),
+        int(longest == 1), _ptr(positions), _ptr(slots), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(inv_freq),
+        int(rotary_dim if inv_freq is not None else 0), _ptr(q_out), dtype_code(q_out.dtype),
+        _ptr(k_cache) if slots is not None else None, _ptr(v_cache) if slots is not None else None, T, num_heads,
+        num_kv_heads, head_dim, hdp, page_size, num_slots, _ptr(err), _stream()), "vl_conv_rows_norm_rope_write")
+    if longest > 1 and taps > 1:
+        short_conv(proj, 0, C, weight, None, state, state_off, cu, state_slots, None, act=False, longest=longest, in_bias=in_bias)
     return q_out
 
 
@@ -506,12 +569,13 @@ def flash_tc5_supported(dtype, head_dim, page_size) -> bool:
 
 
 def flash_prefill_tc5(qkv, out, k_cache, v_cache, block_table, tiles, num_heads, num_kv_heads, head_dim, scale, window, err,
-                      sinks=None):
+                      sinks=None, weighting="softmax", mask_chunk=None, head_bias=None, gate=None):
     """Attention for prompt portions on the tcgen05 tensor cores; `tiles` as for `flash_prefill`,
-    up to 128 tokens each."""
+    up to 128 tokens each.  `weighting`, `mask_chunk` (the `chunk` there), `head_bias`, `gate`: see `_check_variant`."""
     _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, head_dim)
     _need(out, torch.bfloat16, "out", 2); _need(tiles, torch.int32, "tiles", 2)
     _check_sinks(sinks, num_heads)
+    mode, mask_chunk, gate_stride = _check_variant(qkv, num_heads, weighting, mask_chunk, head_bias, gate, sinks)
     if out.shape != (qkv.shape[0], num_heads * head_dim) or tiles.shape[1] != 4:
         raise KernelError("flash_prefill_tc5: shapes disagree")
     if not flash_tc5_supported(qkv.dtype, head_dim, k_cache.shape[2]):
@@ -519,7 +583,8 @@ def flash_prefill_tc5(qkv, out, k_cache, v_cache, block_table, tiles, num_heads,
     _check(_fn("flash_tc5", "vl_flash_prefill_tc5", {"FA_HD": head_dim})(
         _ptr(qkv), qkv.shape[1], _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
         _ptr(tiles), tiles.shape[0], num_heads, num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0],
-        float(scale), int(window or 0), _ptr(err), _ptr(sinks), _stream()), "vl_flash_prefill_tc5")
+        float(scale), int(window or 0), _ptr(err), _ptr(sinks), mode, mask_chunk, _ptr(head_bias), _ptr(gate), gate_stride,
+        _stream()), "vl_flash_prefill_tc5")
     return out
 
 
@@ -737,9 +802,9 @@ def layernorm_add(y, weight, eps, x, cast=None):
     return x
 
 
-def rmsnorm_add(y, weight, eps, mult, x, cast=None):
+def rmsnorm_add(y, weight, eps, mult, x, cast=None, bias=None):
     """x[r] += mult * (y[r] / sqrt(mean(y[r]^2) + eps) * weight), x float32 [R, H], y in the activation dtype; `cast`
-    (same dtype as y, or None) receives the new x."""
+    (same dtype as y, or None) receives the new x.  `bias` (float32 [H] or None) is added to every row of y first."""
     _need(y, None, "y", 2); _need(x, torch.float32, "x", 2); _need(weight, torch.float32, "weight", 1)
     if y.shape != x.shape or weight.shape[0] != x.shape[1]:
         raise KernelError(f"rmsnorm_add: y {tuple(y.shape)}, x {tuple(x.shape)}, weight {tuple(weight.shape)}")
@@ -747,7 +812,11 @@ def rmsnorm_add(y, weight, eps, mult, x, cast=None):
         _need(cast, y.dtype, "cast", 2)
         if cast.shape != x.shape:
             raise KernelError("rmsnorm_add: cast must have the shape of x")
-    _check(_fn("embed_norm", "vl_rmsnorm_add")(_ptr(y), dtype_code(y.dtype), _ptr(weight), float(eps), float(mult), _ptr(x),
+    if bias is not None:
+        _need(bias, torch.float32, "bias", 1)
+        if bias.shape[0] != x.shape[1]:
+            raise KernelError("rmsnorm_add: the bias has one entry per column")
+    _check(_fn("embed_norm", "vl_rmsnorm_add")(_ptr(y), dtype_code(y.dtype), _ptr(bias), _ptr(weight), float(eps), float(mult), _ptr(x),
                                                _ptr(cast), x.shape[0], x.shape[1], _stream()), "vl_rmsnorm_add")
     return x
 
@@ -1215,22 +1284,29 @@ def _seg_args(cu, slots):
     return B
 
 
-def short_conv(x, col0, C, weight, bias, state, state_off, cu, slots, out, act=True, longest=None):
+def short_conv(x, col0, C, weight, bias, state, state_off, cu, slots, out, act=True, longest=None, in_bias=None):
     """out float32 [T, C] = act(causal convolution over time of columns col0 .. col0+C of x [T, ld]); weight float32
     [C, taps]; the last taps-1 inputs live at `state_off` of every request's state row [(taps-1), C].  `longest`: a
-    bound on the tokens one request brings (default: all of them)."""
-    _need(x, None, "x", 2); _need(weight, torch.float32, "weight", 2); _need(out, torch.float32, "out", 2)
+    bound on the tokens one request brings (default: all of them).  `in_bias` (float32 [C] or None) is added to the
+    rows of x as they are read, before the convolution; the state keeps them with it."""
+    _need(x, None, "x", 2); _need(weight, torch.float32, "weight", 2)
     taps = weight.shape[1]
-    if weight.shape[0] != C or out.shape != (x.shape[0], C):
+    if out is not None:                         # None: only the new state is made (the rows were computed elsewhere)
+        _need(out, torch.float32, "out", 2)
+    if weight.shape[0] != C or (out is not None and out.shape != (x.shape[0], C)):
         raise KernelError("short_conv: shapes disagree")
-    if bias is not None:
-        _need(bias, torch.float32, "bias", 1)
+    for t, n in ((bias, "bias"), (in_bias, "in_bias")):
+        if t is not None:
+            _need(t, torch.float32, n, 1)
+            if t.shape[0] != C:
+                raise KernelError(f"short_conv: {n} has one entry per channel")
     B = _seg_args(cu, slots)
     sp, stride = _state_args(state, state_off, (taps - 1) * C)
-    _check(_fn("recurrent", "vl_short_conv")(_ptr(x), dtype_code(x.dtype), x.shape[1], col0, C, _ptr(weight), _ptr(bias), taps,
+    _check(_fn("recurrent", "vl_short_conv")(_ptr(x), dtype_code(x.dtype), x.shape[1], col0, C, _ptr(weight), _ptr(bias),
+                                             _ptr(in_bias), taps,
                                              sp, stride, _ptr(cu), _ptr(slots), B, int(longest or max(x.shape[0], 1)), _ptr(out),
                                              int(bool(act)), _stream()), "vl_short_conv")
-    if int(longest or x.shape[0]) > 64:
+    if out is not None and int(longest or x.shape[0]) > 64:
         global launch_count
         launch_count += 1           # requests cut among blocks: the new state is a launch of its own
     return out

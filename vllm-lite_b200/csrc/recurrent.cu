@@ -8,7 +8,9 @@
 //
 //   vl_short_conv   out[t, c] = act(bias[c] + sum_j w[c, j] in[t - (taps-1) + j, c]), zeros before a request's
 //                   first token; the last taps-1 inputs of every channel are part of the state (`longest`: a bound
-//                   on the tokens a request brings, which says how many blocks share a request)
+//                   on the tokens a request brings, which says how many blocks share a request).  `in_bias`: a
+//                   number per channel added to every input row as it is read (the bias of the product that made
+//                   the rows, left to this kernel); the state keeps the rows with it
 //   vl_token_shift  h[t] = x[t] + (x[t-1] - x[t]) mu, the row before a portion's first token being part of the state
 //   vl_ssd_scan     S <- exp(-exp(A_log) dt) S + dt B x^T,  y = S^T C + D x          (S: N x P per head, dt =
 //                   softplus(raw + bias); heads share B and C in groups)
@@ -78,8 +80,9 @@ static inline bool scan_shape(int N, int P, ScanShape* sh) {
 template <typename TP>
 __global__ void __launch_bounds__(256)
 short_conv_kernel(const TP* __restrict__ in, int ld, int col0, int C, const float* __restrict__ w,
-                  const float* __restrict__ bias, int taps, float* __restrict__ state, long long state_stride,
-                  const int* __restrict__ cu, const int* __restrict__ slots, float* __restrict__ out, int act, int mode) {
+                  const float* __restrict__ bias, const float* __restrict__ in_bias, int taps, float* __restrict__ state,
+                  long long state_stride, const int* __restrict__ cu, const int* __restrict__ slots, float* __restrict__ out,
+                  int act, int mode) {
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.y;
@@ -91,12 +94,13 @@ short_conv_kernel(const TP* __restrict__ in, int ld, int col0, int C, const floa
     const bool live = c < C;
     float* st = state + (long long)slots[b] * state_stride;          // [(taps-1), C]
     const int back = taps - 1;
+    const float ib = (live && in_bias) ? in_bias[c] : 0.f;
     if (live && mode != 2) {
         for (int t = first + threadIdx.y; t < last; t += blockDim.y) {
             float acc = bias ? bias[c] : 0.f;
             for (int j = 0; j < taps; ++j) {
                 const int at = t - back + j;
-                const float v = at >= 0 ? to_f32(in[(size_t)(s0 + at) * ld + col0 + c]) : st[(size_t)(at + back) * C + c];
+                const float v = at >= 0 ? to_f32(in[(size_t)(s0 + at) * ld + col0 + c]) + ib : st[(size_t)(at + back) * C + c];
                 acc += w[(size_t)c * taps + j] * v;
             }
             out[(size_t)(s0 + t) * C + c] = act ? silu_f(acc) : acc;
@@ -107,27 +111,28 @@ short_conv_kernel(const TP* __restrict__ in, int ld, int col0, int C, const floa
     if (live && threadIdx.y == 0) {
         for (int j = 0; j < back; ++j) {                              // reads run ahead of the writes
             const int at = n - back + j;
-            st[(size_t)j * C + c] = at >= 0 ? to_f32(in[(size_t)(s0 + at) * ld + col0 + c]) : st[(size_t)(at + back) * C + c];
+            st[(size_t)j * C + c] = at >= 0 ? to_f32(in[(size_t)(s0 + at) * ld + col0 + c]) + ib : st[(size_t)(at + back) * C + c];
         }
     }
 }
 
 extern "C" int vl_short_conv(const void* in, int dtype, int ld, int col0, int C, const float* w, const float* bias,
-                             int taps, float* state, long long state_stride, const int* cu, const int* slots,
+                             const float* in_bias, int taps, float* state, long long state_stride, const int* cu, const int* slots,
                              int B, int longest, float* out, int act, void* stream) {
     if (B <= 0 || C <= 0) return VL_OK;
     if (taps <= 0 || col0 < 0 || col0 + C > ld || longest <= 0) return VL_ERR_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
     const int cuts = (longest + CONV_TOKENS - 1) / CONV_TOKENS;
-    for (int pass = 0; pass < (cuts > 1 ? 2 : 1); ++pass) {
-        const int mode = cuts > 1 ? pass + 1 : 0;
+    // without `out` only the new state is made (the caller computed the rows itself, from the old state)
+    for (int pass = out ? 0 : 1; pass < (cuts > 1 || !out ? 2 : 1); ++pass) {
+        const int mode = (cuts > 1 || !out) ? pass + 1 : 0;
         dim3 grid((C + 31) / 32, B, mode == 1 ? cuts : 1), block(32, 8);
         int rc;
         if (dtype == VL_F32)
-            rc = vl_launch(short_conv_kernel<float>, grid, block, 0, s, (const float*)in, ld, col0, C, w, bias, taps, state,
+            rc = vl_launch(short_conv_kernel<float>, grid, block, 0, s, (const float*)in, ld, col0, C, w, bias, in_bias, taps, state,
                            state_stride, cu, slots, out, act, mode);
         else if (dtype == VL_BF16)
-            rc = vl_launch(short_conv_kernel<bf16>, grid, block, 0, s, (const bf16*)in, ld, col0, C, w, bias, taps, state,
+            rc = vl_launch(short_conv_kernel<bf16>, grid, block, 0, s, (const bf16*)in, ld, col0, C, w, bias, in_bias, taps, state,
                            state_stride, cu, slots, out, act, mode);
         else
             return VL_ERR_UNSUPPORTED;
@@ -144,7 +149,7 @@ extern "C" int vl_short_conv(const void* in, int dtype, int ld, int col0, int C,
 // A row at a negative position (a padded row of a replayed step) passes unchanged and touches no state.
 template <typename TO>
 __global__ void __launch_bounds__(256)
-token_shift_kernel(const float* __restrict__ x, const float* __restrict__ mu, float* __restrict__ state,
+token_shift_kernel(const float* __restrict__ x, const float* __restrict__ mu, float* state,
                    long long state_stride, const int* __restrict__ cu, const int* __restrict__ slots,
                    const int* __restrict__ req_index, const int* __restrict__ positions, TO* __restrict__ out, int W) {
     pdl_launch_dependents();
@@ -159,17 +164,32 @@ token_shift_kernel(const float* __restrict__ x, const float* __restrict__ mu, fl
         for (int i = threadIdx.x; i < W; i += 256) o[i] = from_f32<TO>(xr[i]);
         return;
     }
-    if (t != first) {
-        const float* before = xr - W;
-        for (int i = threadIdx.x; i < W; i += 256) { const float v = xr[i]; o[i] = from_f32<TO>(v + (before[i] - v) * mu[i]); }
-        return;
-    }
+    const bool head = t == first;                                     // the row before lies in the state
     float* st = state + (long long)slots[b] * state_stride;
     const float* keep = x + (size_t)last * W;
+    if ((W & 3) == 0 && ((((size_t)st) | ((size_t)mu)) & 15) == 0) {  // 16-byte accesses where the state's row allows them
+        for (int i = 4 * threadIdx.x; i < W; i += 1024) {
+            const float4 v = Quad<float>::load(xr + i), m = Quad<float>::load(mu + i);
+            float4 p;
+            if (head) {                                               // the old state first, then the new one
+                p = __ldcg(reinterpret_cast<const float4*>(st + i));
+                const float4 k = Quad<float>::load(keep + i);
+                __threadfence_block();
+                Quad<float>::store(st + i, k);
+            } else {
+                p = Quad<float>::load(xr - W + i);
+            }
+            float4 r;
+            r.x = v.x + (p.x - v.x) * m.x; r.y = v.y + (p.y - v.y) * m.y;
+            r.z = v.z + (p.z - v.z) * m.z; r.w = v.w + (p.w - v.w) * m.w;
+            Quad<TO>::store(o + i, r);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < W; i += 256) {
-        const float v = xr[i], before = st[i];
-        st[i] = keep[i];
-        o[i] = from_f32<TO>(v + (before - v) * mu[i]);
+        const float v = xr[i], p = head ? st[i] : xr[i - W];
+        if (head) st[i] = keep[i];
+        o[i] = from_f32<TO>(v + (p - v) * mu[i]);
     }
 }
 

@@ -250,10 +250,22 @@ extern "C" int vl_qk_norm_rope_write(
 // hdp >= hd is the head size the attention kernels see; features hd .. hdp - 1 are written as zeros.
 // One block per token; sums of squares, angles, sine and cosine in float32.  A token at a negative position
 // (a padded row of a replayed step) gets zeros for q and writes no cache.
+// With CONV the block makes its row itself, in shared memory, from the product `proj` [T, pld] (q | k columns first):
+//   row[c] = sum_j w[c, j] (proj[t - (taps-1) + j, c] + in_bias[c]),   rows before the portion's first token from the
+//   request's state [(taps-1), C] (zeros in a fresh slot), in the order of sums of vl_short_conv (the same bits).
+// `own_state` (every request of the step brings one token): the block also shifts the token's row into the state;
+// else the caller runs vl_short_conv's state pass after this launch.
 // ---------------------------------------------------------------------------------------------------------
-template <typename T>
+struct ConvSource {
+    const void* proj; int pld;                           // the product, its row length
+    const float* w; const float* in_bias; int taps;      // [C, taps], [C] or null
+    float* state; long long state_stride;                // a row per state slot
+    const int* cu; const int* state_slots; const int* req_index;
+    int own_state;
+};
+template <typename T, typename TP, bool CONV>
 __global__ void __launch_bounds__(ROPE_THREADS)
-rows_norm_rope_write_kernel(const float* __restrict__ in, int ld, const int* __restrict__ positions,
+rows_norm_rope_write_kernel(const float* __restrict__ in, int ld, ConvSource cs, const int* __restrict__ positions,
                             const int* __restrict__ slots, const float* __restrict__ qw, const float* __restrict__ kw,
                             float eps, const float* __restrict__ inv_freq, int rot, T* __restrict__ q_out,
                             T* __restrict__ kcache, T* __restrict__ vcache, int nq, int nkv, int hd, int hdp, int page_size,
@@ -276,6 +288,28 @@ rows_norm_rope_write_kernel(const float* __restrict__ in, int ld, const int* __r
         return;
     }
     const float* row = in + (size_t)t * ld;
+    if constexpr (CONV) {
+        extern __shared__ float s_row[];
+        const TP* proj = (const TP*)cs.proj;
+        const int b = cs.req_index[t], s0 = cs.cu[b], i = t - s0, C = Cq + Ck, back = cs.taps - 1;
+        float* st = cs.state + (long long)cs.state_slots[b] * cs.state_stride;
+        for (int c = threadIdx.x; c < C; c += ROPE_THREADS) {
+            const float ib = cs.in_bias ? cs.in_bias[c] : 0.f;
+            float acc = 0.f;
+            for (int j = 0; j < cs.taps; ++j) {
+                const int at = i - back + j;
+                const float v = at >= 0 ? to_f32(proj[(size_t)(s0 + at) * cs.pld + c]) + ib : st[(size_t)(at + back) * C + c];
+                acc += cs.w[(size_t)c * cs.taps + j] * v;
+            }
+            s_row[c] = acc;
+            if (cs.own_state) {                              // one token: rows 1.. move up, the token's row comes last
+                for (int j = 0; j + 1 < back; ++j) st[(size_t)j * C + c] = st[(size_t)(j + 1) * C + c];
+                if (back > 0) st[(size_t)(back - 1) * C + c] = to_f32(proj[(size_t)t * cs.pld + c]) + ib;
+            }
+        }
+        __syncthreads();
+        row = s_row;
+    }
     float ssq = 0.f, ssk = 0.f;
     for (int e = threadIdx.x; e < Cq; e += ROPE_THREADS) { const float v = row[e]; ssq += v * v; }
     for (int e = threadIdx.x; e < Ck; e += ROPE_THREADS) { const float v = row[Cq + e]; ssk += v * v; }
@@ -332,11 +366,55 @@ extern "C" int vl_rows_norm_rope_write(const float* in, int ld, const int* posit
     if (hd <= 0 || hdp < hd || nq <= 0 || nkv <= 0 || rot < 0 || rot > hd || (rot & 1) || rot > ROPE_MAX_HD) return VL_ERR_UNSUPPORTED;
     if (page_size <= 0 || ld < (nq + nkv) * hd || !qw || !kw) return VL_ERR_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
+    const ConvSource none = {};
     if (dtype == VL_F32)
-        return vl_launch(rows_norm_rope_write_kernel<float>, dim3(T), dim3(ROPE_THREADS), 0, s, in, ld, positions, slots, qw, kw,
+        return vl_launch(rows_norm_rope_write_kernel<float, float, false>, dim3(T), dim3(ROPE_THREADS), 0, s, in, ld, none, positions, slots, qw, kw,
                          eps, inv_freq, rot, (float*)q_out, (float*)kcache, (float*)vcache, nq, nkv, hd, hdp, page_size, num_slots, err);
     if (dtype == VL_BF16)
-        return vl_launch(rows_norm_rope_write_kernel<bf16>, dim3(T), dim3(ROPE_THREADS), 0, s, in, ld, positions, slots, qw, kw,
+        return vl_launch(rows_norm_rope_write_kernel<bf16, float, false>, dim3(T), dim3(ROPE_THREADS), 0, s, in, ld, none, positions, slots, qw, kw,
                          eps, inv_freq, rot, (bf16*)q_out, (bf16*)kcache, (bf16*)vcache, nq, nkv, hd, hdp, page_size, num_slots, err);
+    return VL_ERR_UNSUPPORTED;
+}
+
+// Most floats of a row that the fused form keeps in shared memory.
+#define CONV_ROW_MAX (200 * 1024 / 4)
+extern "C" int vl_conv_rows_max() { return CONV_ROW_MAX; }
+
+template <typename T, typename TP>
+static int launch_conv_rows(int T_, size_t smem, cudaStream_t s, const ConvSource& cs, const int* positions, const int* slots,
+                            const float* qw, const float* kw, float eps, const float* inv_freq, int rot, void* q_out, void* kcache,
+                            void* vcache, int nq, int nkv, int hd, int hdp, int page_size, long long num_slots, unsigned* err) {
+    auto kernel = rows_norm_rope_write_kernel<T, TP, true>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return vl_launch(kernel, dim3(T_), dim3(ROPE_THREADS), smem, s, (const float*)nullptr, 0, cs, positions, slots, qw, kw, eps,
+                     inv_freq, rot, (T*)q_out, (T*)kcache, (T*)vcache, nq, nkv, hd, hdp, page_size, num_slots, err);
+}
+
+// The convolution of vl_short_conv and vl_rows_norm_rope_write in one launch (see the kernel's comment); the activation
+// dtype of proj and of the outputs is `dtype`.  `own_state` != 0 only when every request brings exactly one token.
+extern "C" int vl_conv_rows_norm_rope_write(const void* proj, int pld, const float* w, const float* in_bias, int taps, float* state,
+                                            long long state_stride, const int* cu, const int* state_slots, const int* req_index,
+                                            int own_state, const int* positions, const int* slots, const float* qw, const float* kw,
+                                            float eps, const float* inv_freq, int rot, void* q_out, int dtype, void* kcache,
+                                            void* vcache, int T, int nq, int nkv, int hd, int hdp, int page_size, long long num_slots,
+                                            unsigned* err, void* stream) {
+    if (T <= 0) return VL_OK;
+    if (hd <= 0 || hdp < hd || nq <= 0 || nkv <= 0 || rot < 0 || rot > hd || (rot & 1) || rot > ROPE_MAX_HD) return VL_ERR_UNSUPPORTED;
+    const long long C = (long long)(nq + nkv) * hd;
+    if (C > CONV_ROW_MAX) return VL_ERR_UNSUPPORTED;
+    if (page_size <= 0 || pld < C || taps <= 0 || !w || !qw || !kw || !proj || !state || !cu || !state_slots || !req_index ||
+        state_stride < (long long)(taps - 1) * C) return VL_ERR_ARGUMENT;
+    const ConvSource cs = {proj, pld, w, in_bias, taps, state, state_stride, cu, state_slots, req_index, own_state};
+    const size_t smem = (size_t)C * sizeof(float);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VL_F32)
+        return launch_conv_rows<float, float>(T, smem, s, cs, positions, slots, qw, kw, eps, inv_freq, rot, q_out, kcache, vcache,
+                                              nq, nkv, hd, hdp, page_size, num_slots, err);
+    if (dtype == VL_BF16)
+        return launch_conv_rows<bf16, bf16>(T, smem, s, cs, positions, slots, qw, kw, eps, inv_freq, rot, q_out, kcache, vcache,
+                                            nq, nkv, hd, hdp, page_size, num_slots, err);
     return VL_ERR_UNSUPPORTED;
 }

@@ -103,9 +103,10 @@ def run(qkv, out, cache, group, step, spec, scale, fold=None, sinks=None, weight
 
 
 def _run_variant(ops, q, out, cache, group, step, spec, scale, weighting, chunk, head_bias, gate, sinks):
-    """Attention with another weighting than the softmax, a chunked mask or an output gate: in bfloat16 the mma.sync
-    kernels for portions of prompts and the block-per-chunk kernel for single tokens, each with these options; in
-    float32, or where those do not take the head size or the step, the one kernel whose sums depend on positions alone."""
+    """Attention with another weighting than the softmax, a chunked mask or an output gate: in bfloat16 the tensor-core
+    kernels for portions of prompts (tcgen05 for long portions of heads of 64 or 128, else mma.sync) and the
+    block-per-chunk kernel for single tokens, each with these options; in float32, or where those do not take the head
+    size or the step, the one kernel whose sums depend on positions alone."""
     variant = dict(weighting=weighting, mask_chunk=chunk, head_bias=head_bias, gate=gate)
     args = (q, out, cache.k, cache.v, group.block_table, step.req_index, step.positions,
             spec.num_heads, spec.num_kv_heads, spec.head_dim, scale, spec.window)
@@ -115,8 +116,12 @@ def _run_variant(ops, q, out, cache, group, step, spec, scale, weighting, chunk,
                 return _decode(ops, args, step, spec, group, q.shape[0], group.max_context, sinks=sinks, variant=variant)
         elif step.query_tiles is not None and (step.single_tokens is None or _variant_decode_ok(
                 ops, spec, step.single_tokens.shape[0], step.single_context, chunk)):
-            ops.flash_prefill(q, out, cache.k, cache.v, group.block_table, step.query_tiles, spec.num_heads, spec.num_kv_heads,
-                              spec.head_dim, scale, spec.window, step.err, tile_rows=QUERY_TILE, sinks=sinks, **variant)
+            tile_args = (q, out, cache.k, cache.v, group.block_table, step.query_tiles, spec.num_heads, spec.num_kv_heads,
+                         spec.head_dim, scale, spec.window, step.err)
+            if step.max_query_len > 64 and ops.flash_tc5_supported(q.dtype, spec.head_dim, group.page_size):
+                ops.flash_prefill_tc5(*tile_args, sinks=sinks, **variant)
+            else:
+                ops.flash_prefill(*tile_args, tile_rows=QUERY_TILE, sinks=sinks, **variant)
             if step.single_tokens is not None:
                 _decode(ops, args, step, spec, group, step.single_tokens.shape[0], step.single_context,
                         token_index=step.single_tokens, sinks=sinks, variant=variant)

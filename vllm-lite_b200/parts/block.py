@@ -116,6 +116,10 @@ class PostNormBlock:
                 raise TypeError(f"norm kind {norm.spec.kind!r} cannot norm a sub-layer's output into the stream: "
                                 f"it offers no add_normed(y, x, step, cast)")
         self.mult = float(spec.residual_mult)
+        # a mixer whose last product has a bias may leave it to the norm's kernel, which reads that product anyway
+        self.bias1 = None
+        if getattr(self.norm1, "adds_bias", False) and hasattr(self.mixer, "take_out_bias"):
+            self.bias1 = self.mixer.take_out_bias()
         self.graph_safe = bool(getattr(self.mixer, "graph_safe", False)
                                and (self.ffn is None or getattr(self.ffn, "graph_safe", False)))
 
@@ -143,7 +147,7 @@ class PostNormBlock:
             y = self.mixer(h, step, cache)
         # the feed-forward reads the new stream in the activation dtype; after the last norm of the block only a
         # following block that asks for it does
-        residual.cast = self.norm1.add_normed(y, residual.x, step, buf, **kw)
+        residual.cast = self.norm1.add_normed(y, residual.x, step, buf, **kw, **({} if self.bias1 is None else {"bias": self.bias1}))
         if self.ffn is not None:
             h = residual.x if buf is None else residual.cast
             y = self.ffn(h, step)

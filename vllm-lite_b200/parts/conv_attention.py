@@ -1,10 +1,11 @@
 """Attention behind short convolutions, with the keys as values and a choice of weighting.
 
-    [q | k | g] = W h (+ b)       one stacked product: queries, keys, one gate logit per head
-    q, k <- causal convolution over time, per channel (`ops.short_conv`; the last taps - 1 projected rows of a request
-            are part of its state)
+    [q | k | g] = W h             one stacked product: queries, keys, one gate logit per head
+    q, k <- causal convolution over time, per channel, of the product plus its bias (`ops.short_conv` adds the bias
+            as it reads; the last taps - 1 projected rows of a request are part of its state)
     v = k;  q, k <- row / rms(whole row) * weight;  rotation of the first features of every head;  q kept, k and v
-            written to the pages (`ops.rows_norm_rope_write`: one kernel)
+            written to the pages (`ops.conv_rows_norm_rope_write`: one kernel with the convolution; rows too long for
+            its shared memory go through `ops.short_conv` and `ops.rows_norm_rope_write`)
     o_h = sum over the visible keys j of w_j v_j,  w_j = sigmoid(scale q_h.k_j + pb[h])  (or a softmax), keys cut by
             `chunk` and `window`, times sigmoid(g_h)     (the framework's attention kernels with their options)
     out = W_o o (+ b)
@@ -75,19 +76,15 @@ class ConvAttention:
         q, k, g, o, pb = s.names
         f32 = lambda t: t.to(device=ctx.device, dtype=torch.float32).contiguous()
         stack = [weights[q], weights[k]] + ([weights[g]] if s.gate else [])
-        bias = None
-        if s.bias:
-            bias = torch.cat([weights[q + s.bias_suffix].float(), weights[k + s.bias_suffix].float()]
-                             + ([torch.zeros(s.num_heads, device=weights[q].device)] if s.gate else []))
+        # the biases of q and k are added by the convolution's kernel as it reads the product (the gate has none)
+        self.in_bias = f32(torch.cat([weights[q + s.bias_suffix].float(), weights[k + s.bias_suffix].float()])) if s.bias else None
         # the stacked rows are padded to a multiple of 8, so that every row of the product starts on 16 bytes
         width = Cq + Ck + (s.num_heads if s.gate else 0)
         self.width = -(-width // 8) * 8
         w = torch.cat(stack, dim=0)
         if self.width != width:
             w = torch.cat([w, torch.zeros((self.width - width, w.shape[1]), dtype=w.dtype, device=w.device)], dim=0)
-            if bias is not None:
-                bias = torch.cat([bias, torch.zeros(self.width - width, device=bias.device)])
-        self.in_proj = Linear(w.contiguous(), bias)
+        self.in_proj = Linear(w.contiguous())
         wo = weights[o]
         if pd != s.head_dim:                       # zero columns for the padded features of every head
             wp = torch.zeros((wo.shape[0], s.num_heads, pd), dtype=wo.dtype, device=wo.device)
@@ -109,6 +106,12 @@ class ConvAttention:
         import dataclasses
         self.kernel_spec = dataclasses.replace(s, head_dim=pd)
 
+    def take_out_bias(self):
+        """Hands the output projection's bias to the caller (a block whose norm reads the product anyway); the part
+        then returns W_o o alone."""
+        bias, self.o_proj.bias = self.o_proj.bias, None
+        return bias
+
     def __call__(self, h, step, cache):
         from ..csrc import ops
         from . import attention_dispatch
@@ -118,13 +121,20 @@ class ConvAttention:
         T = h.shape[0]
         proj = self.in_proj(h, step, "ca.in")
         C = self.Cq + self.Ck
-        qk = ws.get(tag + "ca.qk", (T, C), torch.float32)
-        ops.short_conv(proj, 0, C, self.taps, None, conv_state.state, 0, step.cu_seqlens, step.state_slots, qk,
-                       act=False, longest=step.max_query_len)
         q = ws.get(tag + "ca.q", (T, s.num_heads * self.pd), self.dtype)
-        ops.rows_norm_rope_write(qk, step.positions, group.slots if pages.writes else None, self.q_norm, self.k_norm, s.eps,
-                                 self.inv_freq, self.rot, q, pages.k, pages.v, s.num_heads, s.num_kv_heads, s.head_dim,
-                                 step.err, padded_head_dim=self.pd)
+        slots = group.slots if pages.writes else None
+        if ops.conv_rows_fused_ok(C):
+            # convolution, norms, rotation and the cache rows in one launch: the convolved row stays on the chip
+            ops.conv_rows_norm_rope_write(proj, self.taps, self.in_bias, conv_state.state, 0, step.cu_seqlens, step.state_slots,
+                                          step.req_index, step.max_query_len, step.positions, slots, self.q_norm, self.k_norm,
+                                          s.eps, self.inv_freq, self.rot, q, pages.k, pages.v, s.num_heads, s.num_kv_heads,
+                                          s.head_dim, step.err, padded_head_dim=self.pd)
+        else:
+            qk = ws.get(tag + "ca.qk", (T, C), torch.float32)
+            ops.short_conv(proj, 0, C, self.taps, None, conv_state.state, 0, step.cu_seqlens, step.state_slots, qk,
+                           act=False, longest=step.max_query_len, in_bias=self.in_bias)
+            ops.rows_norm_rope_write(qk, step.positions, slots, self.q_norm, self.k_norm, s.eps, self.inv_freq, self.rot, q,
+                                     pages.k, pages.v, s.num_heads, s.num_kv_heads, s.head_dim, step.err, padded_head_dim=self.pd)
         out = ws.get(tag + "ca.out", (T, s.num_heads * self.pd), self.dtype)
         gate = proj[:, C:C + s.num_heads] if s.gate else None
         attention_dispatch.run(q, out, pages, group, step, self.kernel_spec, self.scale, weighting=s.weighting,

@@ -25,11 +25,13 @@ class RmsNorm:
         w = weights[spec.tensor].to(device=ctx.device, dtype=torch.float32)
         self.weight = (w.reshape(1).expand(spec.size) if spec.scalar else w).contiguous()
 
-    def add_normed(self, y, x, step, cast=None, mult=1.0):
-        """x += mult * norm(y): what a block that norms its sub-layers' OUTPUTS calls; `cast` (a buffer in the
+    adds_bias = True           # add_normed takes the bias that the sub-layer's last product left out
+
+    def add_normed(self, y, x, step, cast=None, mult=1.0, bias=None):
+        """x += mult * norm(y + bias): what a block that norms its sub-layers' OUTPUTS calls; `cast` (a buffer in the
         activation dtype, or None) receives the new x.  Returns cast."""
         from ..csrc import ops
-        ops.rmsnorm_add(y, self.weight, self.spec.eps, mult, x, cast)
+        ops.rmsnorm_add(y, self.weight, self.spec.eps, mult, x, cast, bias=bias)
         return cast
 
     def fused_rms(self):

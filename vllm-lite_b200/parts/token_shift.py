@@ -45,6 +45,11 @@ class TokenShift:
         self._inner_parts = None if need is None else (len(need.parts) if isinstance(need, Several) else 0)
         self.graph_safe = bool(getattr(self.inner, "graph_safe", False))
 
+    def take_out_bias(self):
+        """The bias of the wrapped mixer's last product, if that mixer can leave it to the caller (else None)."""
+        take = getattr(self.inner, "take_out_bias", None)
+        return take() if take is not None else None
+
     def __call__(self, x, step, cache):
         """x: the float32 stream [T, hidden]."""
         from ..csrc import ops
