@@ -430,7 +430,7 @@ TIMED_OPS = ("paged_attention", "flash_prefill", "flash_prefill_tc5", "flash_dec
              "layernorm_rows", "add_rmsnorm", "latent_norm_write", "qk_norm_rope_write", "moe_route", "moe_align",
              "moe_gather", "moe_combine", "gated_act", "silu_mul", "scale_softcap", "embed", "cast", "add_bias",
              "hc_step", "dyt_rows", "short_conv", "ssd_scan", "mlstm_scan", "delta_scan", "gate_norm", "scaled_sum",
-             "token_shift", "rows_norm_rope_write", "rmsnorm_add", "unary_act")
+             "token_shift", "rows_norm_rope_write", "conv_rows_norm_rope_write", "rmsnorm_add", "unary_act")
 
 
 def kikepel_config(size, layers):
@@ -812,6 +812,9 @@ def sodonex_bench(args):
         # whole-row norm, rotation, cache write: float32 q and k in; q, k and v out in bfloat16
         r["rows_norm_rope_write_gbs"] = gb(count(sx, step, "rows_norm_rope_write") * rows * (C * 4.0 + (H + 2 * KV) * D * 2.0),
                                            us(sx, step, ("rows_norm_rope_write",)))
+        # the two in one launch: the product's q and k columns in (bfloat16); q, k and v out in bfloat16
+        r["conv_rows_norm_rope_write_gbs"] = gb(count(sx, step, "conv_rows_norm_rope_write") * rows * (C * 2.0 + (H + 2 * KV) * D * 2.0),
+                                                us(sx, step, ("conv_rows_norm_rope_write",)))
         r["qwen3_qk_norm_rope_write_gbs"] = gb(count(q, step, "qk_norm_rope_write") * rows * (H + 2 * KV) * D * 4.0,
                                                us(q, step, ("qk_norm_rope_write",)))
         # norm of a sublayer's output added into the stream: y in, x in and out, cast out
