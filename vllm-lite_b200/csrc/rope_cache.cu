@@ -263,8 +263,12 @@ struct ConvSource {
     const int* cu; const int* state_slots; const int* req_index;
     int own_state;
 };
-template <typename T, typename TP, bool CONV>
-__global__ void __launch_bounds__(ROPE_THREADS)
+// NT threads a block, chosen by the row's length alone (rows_threads), so that the order of the sums of squares is a
+// matter of the model's sizes, not of the step.
+static inline int rows_threads(long long C) { return C > 2048 ? 512 : (C > 512 ? 256 : 128); }
+#define ROWS_UNROLL 4
+template <typename T, typename TP, bool CONV, int NT>
+__global__ void __launch_bounds__(NT)
 rows_norm_rope_write_kernel(const float* __restrict__ in, int ld, ConvSource cs, const int* __restrict__ positions,
                             const int* __restrict__ slots, const float* __restrict__ qw, const float* __restrict__ kw,
                             float eps, const float* __restrict__ inv_freq, int rot, T* __restrict__ q_out,
@@ -279,12 +283,12 @@ rows_norm_rope_write_kernel(const float* __restrict__ in, int ld, ConvSource cs,
     const int Cq = nq * hd, Ck = nkv * hd;
     if (inv_freq) {
         const float pos = (float)p;
-        for (int i = threadIdx.x; i < half; i += ROPE_THREADS) sincosf(pos * inv_freq[i], &s_sin[i], &s_cos[i]);
+        for (int i = threadIdx.x; i < half; i += NT) sincosf(pos * inv_freq[i], &s_sin[i], &s_cos[i]);
     }
     pdl_wait();
     T* qo = q_out + (size_t)t * nq * hdp;
     if (p < 0) {
-        for (int e = threadIdx.x; e < nq * hdp; e += ROPE_THREADS) qo[e] = from_f32<T>(0.f);
+        for (int e = threadIdx.x; e < nq * hdp; e += NT) qo[e] = from_f32<T>(0.f);
         return;
     }
     const float* row = in + (size_t)t * ld;
@@ -293,30 +297,55 @@ rows_norm_rope_write_kernel(const float* __restrict__ in, int ld, ConvSource cs,
         const TP* proj = (const TP*)cs.proj;
         const int b = cs.req_index[t], s0 = cs.cu[b], i = t - s0, C = Cq + Ck, back = cs.taps - 1;
         float* st = cs.state + (long long)cs.state_slots[b] * cs.state_stride;
-        for (int c = threadIdx.x; c < C; c += ROPE_THREADS) {
-            const float ib = cs.in_bias ? cs.in_bias[c] : 0.f;
-            float acc = 0.f;
+        // ROWS_UNROLL channels a thread at a time, their loads in flight together; a channel's sum runs over the taps in order
+        for (int c0 = threadIdx.x; c0 < C; c0 += NT * ROWS_UNROLL) {
+            float acc[ROWS_UNROLL], ib[ROWS_UNROLL];
+#pragma unroll
+            for (int u = 0; u < ROWS_UNROLL; ++u) {
+                const int c = c0 + u * NT;
+                acc[u] = 0.f;
+                ib[u] = (cs.in_bias && c < C) ? cs.in_bias[c] : 0.f;
+            }
             for (int j = 0; j < cs.taps; ++j) {
                 const int at = i - back + j;
-                const float v = at >= 0 ? to_f32(proj[(size_t)(s0 + at) * cs.pld + c]) + ib : st[(size_t)(at + back) * C + c];
-                acc += cs.w[(size_t)c * cs.taps + j] * v;
+#pragma unroll
+                for (int u = 0; u < ROWS_UNROLL; ++u) {
+                    const int c = c0 + u * NT;
+                    if (c < C) {
+                        const float v = at >= 0 ? to_f32(proj[(size_t)(s0 + at) * cs.pld + c]) + ib[u] : st[(size_t)(at + back) * C + c];
+                        acc[u] += cs.w[(size_t)c * cs.taps + j] * v;
+                    }
+                }
             }
-            s_row[c] = acc;
-            if (cs.own_state) {                              // one token: rows 1.. move up, the token's row comes last
-                for (int j = 0; j + 1 < back; ++j) st[(size_t)j * C + c] = st[(size_t)(j + 1) * C + c];
-                if (back > 0) st[(size_t)(back - 1) * C + c] = to_f32(proj[(size_t)t * cs.pld + c]) + ib;
+#pragma unroll
+            for (int u = 0; u < ROWS_UNROLL; ++u)
+                if (c0 + u * NT < C) s_row[c0 + u * NT] = acc[u];
+            if (cs.own_state && back > 0) {                  // one token: rows 1.. move up, the token's row comes last
+                for (int j = 0; j + 1 < back; ++j) {
+                    float up[ROWS_UNROLL];
+#pragma unroll
+                    for (int u = 0; u < ROWS_UNROLL; ++u)
+                        if (c0 + u * NT < C) up[u] = st[(size_t)(j + 1) * C + c0 + u * NT];
+#pragma unroll
+                    for (int u = 0; u < ROWS_UNROLL; ++u)
+                        if (c0 + u * NT < C) st[(size_t)j * C + c0 + u * NT] = up[u];
+                }
+#pragma unroll
+                for (int u = 0; u < ROWS_UNROLL; ++u)
+                    if (c0 + u * NT < C)
+                        st[(size_t)(back - 1) * C + c0 + u * NT] = to_f32(proj[(size_t)t * cs.pld + c0 + u * NT]) + ib[u];
             }
         }
         __syncthreads();
         row = s_row;
     }
     float ssq = 0.f, ssk = 0.f;
-    for (int e = threadIdx.x; e < Cq; e += ROPE_THREADS) { const float v = row[e]; ssq += v * v; }
-    for (int e = threadIdx.x; e < Ck; e += ROPE_THREADS) { const float v = row[Cq + e]; ssk += v * v; }
-    ssq = block_sum<ROPE_THREADS>(ssq, scratch);
-    ssk = block_sum<ROPE_THREADS>(ssk, scratch);          // (block_sum's own barriers order the table above, too)
+    for (int e = threadIdx.x; e < Cq; e += NT) { const float v = row[e]; ssq += v * v; }
+    for (int e = threadIdx.x; e < Ck; e += NT) { const float v = row[Cq + e]; ssk += v * v; }
+    ssq = block_sum<NT>(ssq, scratch);
+    ssk = block_sum<NT>(ssk, scratch);          // (block_sum's own barriers order the table above, too)
     const float invq = 1.0f / sqrtf(ssq / (float)Cq + eps), invk = 1.0f / sqrtf(ssk / (float)Ck + eps);
-    for (int o = threadIdx.x; o < nq * hdp; o += ROPE_THREADS) {
+    for (int o = threadIdx.x; o < nq * hdp; o += NT) {
         const int h = o / hdp, d = o - h * hdp, e = h * hd + d;
         float v = 0.f;
         if (d < hd) {
@@ -339,7 +368,7 @@ rows_norm_rope_write_kernel(const float* __restrict__ in, int ld, ConvSource cs,
     }
     const int page = slot / page_size, off = slot - page * page_size;
     const float* krow = row + Cq;
-    for (int o = threadIdx.x; o < nkv * hdp; o += ROPE_THREADS) {
+    for (int o = threadIdx.x; o < nkv * hdp; o += NT) {
         const int kvh = o / hdp, d = o - kvh * hdp, e = kvh * hd + d;
         float v = 0.f, raw = 0.f;
         if (d < hd) {
@@ -367,12 +396,21 @@ extern "C" int vl_rows_norm_rope_write(const float* in, int ld, const int* posit
     if (page_size <= 0 || ld < (nq + nkv) * hd || !qw || !kw) return VL_ERR_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
     const ConvSource none = {};
-    if (dtype == VL_F32)
-        return vl_launch(rows_norm_rope_write_kernel<float, float, false>, dim3(T), dim3(ROPE_THREADS), 0, s, in, ld, none, positions, slots, qw, kw,
-                         eps, inv_freq, rot, (float*)q_out, (float*)kcache, (float*)vcache, nq, nkv, hd, hdp, page_size, num_slots, err);
-    if (dtype == VL_BF16)
-        return vl_launch(rows_norm_rope_write_kernel<bf16, float, false>, dim3(T), dim3(ROPE_THREADS), 0, s, in, ld, none, positions, slots, qw, kw,
-                         eps, inv_freq, rot, (bf16*)q_out, (bf16*)kcache, (bf16*)vcache, nq, nkv, hd, hdp, page_size, num_slots, err);
+    const int nt = rows_threads((long long)(nq + nkv) * hd);
+#define ROWS_LAUNCH(TT, NTH)                                                                                            \
+    return vl_launch(rows_norm_rope_write_kernel<TT, float, false, NTH>, dim3(T), dim3(NTH), 0, s, in, ld, none, positions, slots, \
+                     qw, kw, eps, inv_freq, rot, (TT*)q_out, (TT*)kcache, (TT*)vcache, nq, nkv, hd, hdp, page_size, num_slots, err)
+    if (dtype == VL_F32) {
+        if (nt == 512) ROWS_LAUNCH(float, 512);
+        if (nt == 256) ROWS_LAUNCH(float, 256);
+        ROWS_LAUNCH(float, 128);
+    }
+    if (dtype == VL_BF16) {
+        if (nt == 512) ROWS_LAUNCH(bf16, 512);
+        if (nt == 256) ROWS_LAUNCH(bf16, 256);
+        ROWS_LAUNCH(bf16, 128);
+    }
+#undef ROWS_LAUNCH
     return VL_ERR_UNSUPPORTED;
 }
 
@@ -380,16 +418,16 @@ extern "C" int vl_rows_norm_rope_write(const float* in, int ld, const int* posit
 #define CONV_ROW_MAX (200 * 1024 / 4)
 extern "C" int vl_conv_rows_max() { return CONV_ROW_MAX; }
 
-template <typename T, typename TP>
+template <typename T, typename TP, int NT>
 static int launch_conv_rows(int T_, size_t smem, cudaStream_t s, const ConvSource& cs, const int* positions, const int* slots,
                             const float* qw, const float* kw, float eps, const float* inv_freq, int rot, void* q_out, void* kcache,
                             void* vcache, int nq, int nkv, int hd, int hdp, int page_size, long long num_slots, unsigned* err) {
-    auto kernel = rows_norm_rope_write_kernel<T, TP, true>;
+    auto kernel = rows_norm_rope_write_kernel<T, TP, true, NT>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    return vl_launch(kernel, dim3(T_), dim3(ROPE_THREADS), smem, s, (const float*)nullptr, 0, cs, positions, slots, qw, kw, eps,
+    return vl_launch(kernel, dim3(T_), dim3(NT), smem, s, (const float*)nullptr, 0, cs, positions, slots, qw, kw, eps,
                      inv_freq, rot, (T*)q_out, (T*)kcache, (T*)vcache, nq, nkv, hd, hdp, page_size, num_slots, err);
 }
 
@@ -410,11 +448,20 @@ extern "C" int vl_conv_rows_norm_rope_write(const void* proj, int pld, const flo
     const ConvSource cs = {proj, pld, w, in_bias, taps, state, state_stride, cu, state_slots, req_index, own_state};
     const size_t smem = (size_t)C * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == VL_F32)
-        return launch_conv_rows<float, float>(T, smem, s, cs, positions, slots, qw, kw, eps, inv_freq, rot, q_out, kcache, vcache,
-                                              nq, nkv, hd, hdp, page_size, num_slots, err);
-    if (dtype == VL_BF16)
-        return launch_conv_rows<bf16, bf16>(T, smem, s, cs, positions, slots, qw, kw, eps, inv_freq, rot, q_out, kcache, vcache,
-                                            nq, nkv, hd, hdp, page_size, num_slots, err);
+    const int nt = rows_threads(C);
+#define CONV_ROWS_LAUNCH(TT, NTH)                                                                                       \
+    return launch_conv_rows<TT, TT, NTH>(T, smem, s, cs, positions, slots, qw, kw, eps, inv_freq, rot, q_out, kcache, vcache, \
+                                         nq, nkv, hd, hdp, page_size, num_slots, err)
+    if (dtype == VL_F32) {
+        if (nt == 512) CONV_ROWS_LAUNCH(float, 512);
+        if (nt == 256) CONV_ROWS_LAUNCH(float, 256);
+        CONV_ROWS_LAUNCH(float, 128);
+    }
+    if (dtype == VL_BF16) {
+        if (nt == 512) CONV_ROWS_LAUNCH(bf16, 512);
+        if (nt == 256) CONV_ROWS_LAUNCH(bf16, 256);
+        CONV_ROWS_LAUNCH(bf16, 128);
+    }
+#undef CONV_ROWS_LAUNCH
     return VL_ERR_UNSUPPORTED;
 }

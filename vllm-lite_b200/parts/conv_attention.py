@@ -4,8 +4,8 @@
     q, k <- causal convolution over time, per channel, of the product plus its bias (`ops.short_conv` adds the bias
             as it reads; the last taps - 1 projected rows of a request are part of its state)
     v = k;  q, k <- row / rms(whole row) * weight;  rotation of the first features of every head;  q kept, k and v
-            written to the pages (`ops.conv_rows_norm_rope_write`: one kernel with the convolution; rows too long for
-            its shared memory go through `ops.short_conv` and `ops.rows_norm_rope_write`)
+            written to the pages (steps of single tokens: `ops.conv_rows_norm_rope_write`, one kernel with the
+            convolution; other steps: `ops.short_conv`, then `ops.rows_norm_rope_write`; the same bits)
     o_h = sum over the visible keys j of w_j v_j,  w_j = sigmoid(scale q_h.k_j + pb[h])  (or a softmax), keys cut by
             `chunk` and `window`, times sigmoid(g_h)     (the framework's attention kernels with their options)
     out = W_o o (+ b)
@@ -123,8 +123,10 @@ class ConvAttention:
         C = self.Cq + self.Ck
         q = ws.get(tag + "ca.q", (T, s.num_heads * self.pd), self.dtype)
         slots = group.slots if pages.writes else None
-        if ops.conv_rows_fused_ok(C):
-            # convolution, norms, rotation and the cache rows in one launch: the convolved row stays on the chip
+        if step.max_query_len == 1 and ops.conv_rows_fused_ok(C):
+            # single tokens: convolution, norms, rotation and the cache rows in one launch, the convolved row stays on
+            # the chip.  (Portions of prompts go through the two kernels, the same bits: the convolution's kernel
+            # shares a channel's taps among 64 tokens, the one launch would fetch them for every token.)
             ops.conv_rows_norm_rope_write(proj, self.taps, self.in_bias, conv_state.state, 0, step.cu_seqlens, step.state_slots,
                                           step.req_index, step.max_query_len, step.positions, slots, self.q_norm, self.k_norm,
                                           s.eps, self.inv_freq, self.rot, q, pages.k, pages.v, s.num_heads, s.num_kv_heads,
