@@ -399,7 +399,7 @@ def test_convolution_without_bias_or_activation(taps, C, in_bias):
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H_,G_,D_,rot,base", [(4, 2, 16, 8, 10000.0), (2, 1, 24, 24, 500.0), (3, 3, 20, 6, 50.0),
-                                               (8, 2, 64, 32, 200000.0), (1, 1, 128, 2, 7.0)])
+                                               (8, 2, 64, 32, 200000.0), (1, 1, 128, 2, 7.0), (40, 8, 64, 32, 10000.0)])
 def test_whole_row_norm_rotation_and_cache_rows(dtype, H_, G_, D_, rot, base):
     """q and k are normed over the WHOLE row (a norm per head would be far off: the heads are given unequal sizes), the
     first `rot` features of every head turn by the position, the values are the keys as they came, and padded features
@@ -439,7 +439,8 @@ def test_whole_row_norm_rotation_and_cache_rows(dtype, H_, G_, D_, rot, base):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H_,G_,D_,rot,taps", [(4, 2, 16, 8, 3), (2, 1, 24, 24, 1), (3, 3, 20, 6, 6), (8, 2, 64, 32, 4), (1, 1, 128, 2, 2)])
+@pytest.mark.parametrize("H_,G_,D_,rot,taps", [(4, 2, 16, 8, 3), (2, 1, 24, 24, 1), (3, 3, 20, 6, 6), (8, 2, 64, 32, 4), (1, 1, 128, 2, 2),
+                                                (36, 4, 64, 16, 3)])
 def test_convolution_folded_into_the_row_kernel(dtype, H_, G_, D_, rot, taps):
     """The convolution, the whole-row norms, the rotation and the cache rows in one launch against the two kernels in
     turn, bit for bit: two requests in portions and single tokens (the launch renews the state itself when every request
