@@ -7,3 +7,4 @@ from . import qwen3_plan as _qwen3_plan  # noqa: F401  (registers Qwen3ForCausal
 from .kikepel import KikepelConfig  # noqa: F401,E402  (registers Kikepel)
 from .tuzisun import TuzisunConfig  # noqa: F401,E402  (registers Tuzisun)
 from .sodonex import SodonexConfig  # noqa: F401,E402  (registers Sodonex)
+from .puturax import PuturaxConfig  # noqa: F401,E402  (registers Puturax)

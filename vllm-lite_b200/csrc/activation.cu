@@ -134,8 +134,8 @@ extern "C" int vl_gated_act(const void* gu, void* out, int dtype, int T, int I, 
     return VL_ERR_UNSUPPORTED;
 }
 
-// A function of one argument, element by element in float32: act 16 = the square of max(v, 0) (the codes continue
-// those of the gated activations, which take two).
+// A function of one argument, element by element in float32: act 16 = the square of max(v, 0), 17 = tanh(v) (the codes
+// continue those of the gated activations, which take two).
 template <typename T>
 __global__ void unary_act_kernel(const T* __restrict__ in, T* __restrict__ out, size_t n, int act) {
     pdl_launch_dependents();
@@ -144,12 +144,13 @@ __global__ void unary_act_kernel(const T* __restrict__ in, T* __restrict__ out, 
     if (i >= n) return;
     float v = to_f32(in[i]);
     if (act == 16) { v = fmaxf(v, 0.f); v = v * v; }
+    else if (act == 17) v = tanhf(v);
     out[i] = from_f32<T>(v);
 }
 
 extern "C" int vl_unary_act(const void* in, void* out, int dtype, long long n, int act, void* stream) {
     if (n <= 0) return VL_OK;
-    if (act != 16) return VL_ERR_ARGUMENT;
+    if (act != 16 && act != 17) return VL_ERR_ARGUMENT;
     const unsigned blocks = (unsigned)((n + 255) / 256);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VL_F32) return vl_launch(unary_act_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)in, (float*)out, (size_t)n, act);
@@ -191,5 +192,31 @@ extern "C" int vl_scaled_sum(const void* a, float sa, const void* b, float sb, v
         return vl_launch(scaled_sum_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)a, sa, (const float*)b, sb, (float*)out, (size_t)n);
     if (dtype == VL_BF16)
         return vl_launch(scaled_sum_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (const bf16*)a, sa, (const bf16*)b, sb, (bf16*)out, (size_t)n);
+    return VL_ERR_UNSUPPORTED;
+}
+
+// x[t, i] <- x[t, i] * sigmoid(g[t, gcol + i]) for i < n, element by element in float32 (an output gate on the
+// concatenated heads of an attention; x rows ldx wide, g rows ldg wide).
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ x, int ldx, const T* __restrict__ g, int ldg, int gcol, int n, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (idx >= total) return;
+    const size_t t = idx / n;
+    const int i = (int)(idx - t * n);
+    const float gate = 1.0f / (1.0f + expf(-to_f32(g[t * ldg + gcol + i])));
+    T* p = x + t * ldx + i;
+    *p = from_f32<T>(to_f32(*p) * gate);
+}
+
+extern "C" int vl_sigmoid_gate(void* x, int ldx, const void* g, int ldg, int gcol, int dtype, int T, int n, void* stream) {
+    if (T <= 0 || n <= 0) return VL_OK;
+    if (ldx < n || gcol < 0 || ldg < gcol + n) return VL_ERR_ARGUMENT;
+    const size_t total = (size_t)T * n;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VL_F32) return vl_launch(sigmoid_gate_kernel<float>, dim3(blocks), dim3(256), 0, s, (float*)x, ldx, (const float*)g, ldg, gcol, n, total);
+    if (dtype == VL_BF16) return vl_launch(sigmoid_gate_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (bf16*)x, ldx, (const bf16*)g, ldg, gcol, n, total);
     return VL_ERR_UNSUPPORTED;
 }

@@ -13,6 +13,8 @@
 // token, and a query reads no key of an earlier block (lo is then at least the start of the query's block); `gate`
 // multiplies head h's output for token t by sigmoid(gate[t * gate_stride + h]).  Weighting ATT_SIGMOID replaces the
 // softmax: every visible key weighs sigmoid(s_j + head_bias[h]) by itself and nothing is divided by a sum.
+// `softcap` > 0 bounds a score, s <- softcap tanh(s / softcap); `dist_a`, `dist_b` (a number per query head each) then take
+// dist_a[h] ln(1 + dist_b[h] (i - j)) off the score of a key that lies i - j positions back.
 //
 // vl_paged_attention: one block per (token, query head), 16 groups of 8 lanes.
 // Group g owns the keys whose position is g modulo 16 and keeps a running
@@ -47,7 +49,8 @@ paged_attention_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
                        const int* __restrict__ req_index, const int* __restrict__ positions,
                        int nq, int nkv, int page_size, int num_pages, float scale, int window,
                        const float* __restrict__ sinks, int chunk, const float* __restrict__ head_bias,
-                       const T* __restrict__ gate, int gate_stride, unsigned* err) {
+                       const T* __restrict__ gate, int gate_stride, float softcap,
+                       const float* __restrict__ dist_a, const float* __restrict__ dist_b, unsigned* err) {
     constexpr int HD = R * 16;
     __shared__ float s_acc[ATT_GROUPS][HD];
     __shared__ float s_m[ATT_GROUPS], s_l[ATT_GROUPS];
@@ -60,6 +63,8 @@ paged_attention_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
     if (chunk > 0 && pos >= 0) lo = max(lo, pos / chunk * chunk);
     const int* table = block_table + (size_t)req * max_blocks;
     const float hb = (MODE == ATT_SIGMOID && head_bias) ? head_bias[h] : 0.f;
+    const float da = dist_a ? dist_a[h] : 0.f, db = dist_a ? dist_b[h] : 0.f;
+    const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
 
     float qr[R][2], acc[R][2];
     const T* qp = q + (size_t)t * q_stride + (size_t)h * HD;
@@ -98,8 +103,11 @@ paged_attention_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
         dot += __shfl_xor_sync(0xffffffffu, dot, 4);
         dot += __shfl_xor_sync(0xffffffffu, dot, 2);
         dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        float sc = dot * scale;
+        if (softcap > 0.f) sc = softcap * tanhf(sc * inv_cap);
+        if (dist_a && valid) sc -= da * log1pf(db * (float)(pos - j));
         if (valid && MODE == ATT_SIGMOID) {
-            const float p = 1.0f / (1.0f + expf(-(dot * scale + hb)));
+            const float p = 1.0f / (1.0f + expf(-(sc + hb)));
             const T* vp = vcache + base;
 #pragma unroll
             for (int r = 0; r < R; ++r) {
@@ -108,7 +116,7 @@ paged_attention_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
                 acc[r][1] += p * vv.y;
             }
         } else if (valid) {
-            const float s = dot * scale;
+            const float s = sc;
             const float mn = fmaxf(m, s);
             const float corr = expf(m - mn);
             const float p = expf(s - mn);
@@ -167,17 +175,18 @@ static int launch_paged_attention(int R, dim3 grid, cudaStream_t s, const T* q, 
                                   const T* kc, const T* vc, const int* bt, int max_blocks,
                                   const int* req, const int* pos, int nq, int nkv, int page_size,
                                   int num_pages, float scale, int window, const float* sinks, int mode, int chunk,
-                                  const float* head_bias, const T* gate, int gate_stride, unsigned* err) {
+                                  const float* head_bias, const T* gate, int gate_stride, float softcap,
+                                  const float* dist_a, const float* dist_b, unsigned* err) {
 #define ATT_CASE(RR)                                                                              \
     case RR:                                                                                      \
         if (mode == ATT_SIGMOID)                                                                  \
             paged_attention_kernel<T, RR, ATT_SIGMOID><<<grid, ATT_THREADS, 0, s>>>(              \
                 q, q_stride, out, kc, vc, bt, max_blocks, req, pos, nq, nkv, page_size, num_pages,\
-                scale, window, sinks, chunk, head_bias, gate, gate_stride, err);                  \
+                scale, window, sinks, chunk, head_bias, gate, gate_stride, softcap, dist_a, dist_b, err);                \
         else                                                                                      \
             paged_attention_kernel<T, RR, ATT_SOFTMAX><<<grid, ATT_THREADS, 0, s>>>(              \
                 q, q_stride, out, kc, vc, bt, max_blocks, req, pos, nq, nkv, page_size, num_pages,\
-                scale, window, sinks, chunk, head_bias, gate, gate_stride, err);                  \
+                scale, window, sinks, chunk, head_bias, gate, gate_stride, softcap, dist_a, dist_b, err);                \
         break;
     switch (R) {
         ATT_CASE(1) ATT_CASE(2) ATT_CASE(3) ATT_CASE(4) ATT_CASE(5) ATT_CASE(6) ATT_CASE(7) ATT_CASE(8)
@@ -194,8 +203,10 @@ extern "C" int vl_paged_attention(const void* q, int q_stride, void* out, int dt
                                   const int* req_index, const int* positions,
                                   int T, int nq, int nkv, int hd, int page_size, int num_pages,
                                   float scale, int window, const float* sinks, int mode, int chunk,
-                                  const float* head_bias, const void* gate, int gate_stride, unsigned* err, void* stream) {
+                                  const float* head_bias, const void* gate, int gate_stride, float softcap,
+                                  const float* dist_a, const float* dist_b, unsigned* err, void* stream) {
     if (T <= 0) return VL_OK;
+    if ((dist_a == nullptr) != (dist_b == nullptr) || softcap < 0.f) return VL_ERR_ARGUMENT;
     if (hd <= 0 || hd % 16 || hd > ATT_MAX_HD) return VL_ERR_UNSUPPORTED;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0) return VL_ERR_ARGUMENT;
     if ((mode != ATT_SOFTMAX && mode != ATT_SIGMOID) || chunk < 0 || (mode == ATT_SIGMOID && sinks)) return VL_ERR_ARGUMENT;
@@ -208,13 +219,13 @@ extern "C" int vl_paged_attention(const void* q, int q_stride, void* out, int dt
                                              (const float*)kcache, (const float*)vcache, block_table,
                                              max_blocks, req_index, positions, nq, nkv, page_size,
                                              num_pages, scale, window, sinks, mode, chunk, head_bias,
-                                             (const float*)gate, gate_stride, err);
+                                             (const float*)gate, gate_stride, softcap, dist_a, dist_b, err);
     if (dtype == VL_BF16)
         return launch_paged_attention<bf16>(hd / 16, grid, s, (const bf16*)q, q_stride, (bf16*)out,
                                             (const bf16*)kcache, (const bf16*)vcache, block_table,
                                             max_blocks, req_index, positions, nq, nkv, page_size,
                                             num_pages, scale, window, sinks, mode, chunk, head_bias,
-                                            (const bf16*)gate, gate_stride, err);
+                                            (const bf16*)gate, gate_stride, softcap, dist_a, dist_b, err);
     return VL_ERR_UNSUPPORTED;
 }
 

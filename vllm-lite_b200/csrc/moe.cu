@@ -4,7 +4,10 @@
 //
 //   vl_moe_route    from the logits z = W_r h (+ bias) (float32, a product of csrc/gemm_batched.cu): score =
 //                   sigmoid(z) or softmax(z); the `top` largest pick the experts of a token (ties: the
-//                   lower index), weights = the scores as they are or divided by their sum.
+//                   lower index), weights = the scores as they are or divided by their sum (+ renorm_eps).
+//                   `choice_bias` (a number per expert): the choice, also that of the groups, is made on
+//                   score + choice_bias instead of the logits; the weights stay the scores without it.
+//                   `group_top`: a group counts by the sum of its `group_top` largest choice values (1: its largest).
 //                   -> expert ids [T, top], weights float32 [T, top]
 //   vl_moe_align    sorts the T * top (token, choice) pairs by expert into tiles of `bm` rows, every
 //                   expert's rows padded up to whole tiles: sorted_rows[r] = pair or -1,
@@ -27,8 +30,9 @@
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ z, int slices, int ntok, int E, int top,
                  int score_fn, int renorm, int groups, int keep, const float* __restrict__ bias,
+                 const float* __restrict__ choice_bias, int group_top, float renorm_eps,
                  int* __restrict__ ids, float* __restrict__ weights) {
-    extern __shared__ float s_scores[];                  // [4][E], then [4][groups] when the experts form groups
+    extern __shared__ float s_scores[];                  // [4][E], then [4][groups], then [4][E] logits kept for the weights
     pdl_launch_dependents();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -50,6 +54,17 @@ moe_route_kernel(const float* __restrict__ z, int slices, int ntok, int E, int t
         for (int e = lane; e < E; e += 32) zsum += expf(sc[e] - zmax);
         zsum = warp_sum(zsum);
     }
+    float* zl = sc;                                      // where a chosen expert's logit is read for its weight
+    if (choice_bias) {
+        // the choice runs on score + choice_bias (which is not monotone in the logit across experts); the logits are kept
+        zl = s_scores + (size_t)4 * E + (size_t)4 * groups + (size_t)warp * E;
+        for (int e = lane; e < E; e += 32) {
+            const float v = sc[e];
+            zl[e] = v;
+            sc[e] = (score_fn == MOE_SCORE_SOFTMAX ? expf(v - zmax) / zsum : 1.0f / (1.0f + expf(-v))) + choice_bias[e];
+        }
+        __syncwarp();
+    }
     if (groups > 1) {
         // A group counts by its largest logit; experts outside the `keep` best groups (ties: the lower group) cannot
         // be chosen.  The scores above were taken over all experts.
@@ -58,6 +73,23 @@ moe_route_kernel(const float* __restrict__ z, int slices, int ntok, int E, int t
         for (int g = lane; g < groups; g += 32) {
             float m = -INFINITY;
             for (int e = g * per; e < (g + 1) * per; ++e) m = fmaxf(m, sc[e]);
+            if (group_top > 1) {
+                // the sum of the group's largest values, taken one by one (ties: the lower index first)
+                float sum = 0.f, last = INFINITY;
+                int last_e = -1;
+                for (int j = 0; j < group_top && j < per; ++j) {
+                    float best = -INFINITY;
+                    int arg = -1;
+                    for (int e = g * per; e < (g + 1) * per; ++e) {
+                        const float v = sc[e];
+                        const bool after = v < last || (v == last && e > last_e);
+                        if (after && v > best) { best = v; arg = e; }
+                    }
+                    if (arg < 0) break;
+                    sum += best; last = best; last_e = arg;
+                }
+                m = sum;
+            }
             gm[g] = m;
         }
         __syncwarp();
@@ -83,7 +115,8 @@ moe_route_kernel(const float* __restrict__ z, int slices, int ntok, int E, int t
             const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
             if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
         }
-        const float score = score_fn == MOE_SCORE_SOFTMAX ? expf(best - zmax) / zsum : 1.0f / (1.0f + expf(-best));
+        const float zb = zl[arg];
+        const float score = score_fn == MOE_SCORE_SOFTMAX ? expf(zb - zmax) / zsum : 1.0f / (1.0f + expf(-zb));
         if (lane == 0) {
             ids[(size_t)t * top + j] = arg;
             weights[(size_t)t * top + j] = score;
@@ -93,7 +126,7 @@ moe_route_kernel(const float* __restrict__ z, int slices, int ntok, int E, int t
         __syncwarp();
     }
     if (renorm && lane == 0)
-        for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] /= total;
+        for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] /= (total + renorm_eps);
 }
 
 __global__ void __launch_bounds__(1024)
@@ -199,13 +232,16 @@ __global__ void moe_combine_kernel(const T* __restrict__ result, const int* __re
 }
 
 extern "C" int vl_moe_route(const float* z, int slices, int T, int E, int top, int score_fn, int renorm, int groups, int keep,
-                            const float* bias, int* ids, float* weights, void* stream) {
+                            const float* bias, const float* choice_bias, int group_top, float renorm_eps, int* ids,
+                            float* weights, void* stream) {
     if (T <= 0) return VL_OK;
+    if (group_top < 1 || renorm_eps < 0.f) return VL_ERR_ARGUMENT;
     if (E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > E || slices <= 0) return VL_ERR_ARGUMENT;
     if (score_fn != MOE_SCORE_SIGMOID && score_fn != MOE_SCORE_SOFTMAX) return VL_ERR_ARGUMENT;
     if (groups < 1 || E % groups || keep < 1 || keep > groups || keep * (E / groups) < top) return VL_ERR_ARGUMENT;
-    return vl_launch(moe_route_kernel, dim3((T + 3) / 4), dim3(128), (size_t)4 * (E + groups) * sizeof(float),
-                     (cudaStream_t)stream, z, slices, T, E, top, score_fn, renorm, groups, keep, bias, ids, weights);
+    return vl_launch(moe_route_kernel, dim3((T + 3) / 4), dim3(128), (size_t)4 * (E + groups + (choice_bias ? E : 0)) * sizeof(float),
+                     (cudaStream_t)stream, z, slices, T, E, top, score_fn, renorm, groups, keep, bias, choice_bias, group_top,
+                     renorm_eps, ids, weights);
 }
 
 // cap = rows of the sorted buffer (a multiple of bm, at least npairs rounded up per expert: npairs + E * (bm - 1)

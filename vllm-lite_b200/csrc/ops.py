@@ -42,7 +42,18 @@ _SIGNATURES = {
                                               c_void_p, c_void_p],
     ("attention", "vl_paged_attention"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                          c_float, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+                                          c_float, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p,
+                                          c_void_p, c_void_p],
+    ("rope_cache", "vl_head_norm_write"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int,
+                                           c_float, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong,
+                                           c_int, c_void_p, c_void_p],
+    ("latent", "vl_rope_heads"): [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    ("activation", "vl_sigmoid_gate"): [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    ("recurrent", "vl_token_shift_multi"): [c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
+                                            c_void_p, c_int, c_int, c_int, c_void_p],
+    ("recurrent", "vl_decay_scan"): [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
+                                     c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                     c_int, c_int, c_void_p],
     ("rope_cache", "vl_conv_rows_norm_rope_write"): [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p,
                                                      c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
                                                      c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
@@ -83,14 +94,14 @@ _SIGNATURES = {
     ("embed_norm", "vl_layernorm_add"): [c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p],
     ("embed_norm", "vl_layernorm_rows"): [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
     ("latent", "vl_latent_norm_write"): [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
-                                         c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p],
+                                         c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     ("gemm_batched", "vl_gemm_batched_nt"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                              c_longlong, c_longlong, c_longlong, c_int, c_void_p, c_longlong, c_int, c_void_p],
     ("gemm_batched", "vl_gemm_grouped_fused"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                                 c_longlong, c_int, c_void_p, c_int, c_void_p, c_int, c_float, c_float, c_float,
                                                 c_void_p],
-    ("moe", "vl_moe_route"): [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                              c_void_p],
+    ("moe", "vl_moe_route"): [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float,
+                              c_void_p, c_void_p, c_void_p],
     ("gemm_batched", "vl_gemm_rows_f32w"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     ("gemm_tc5_grouped", "vl_gemm_bf16_tc5_grouped"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                                        c_void_p, c_int, c_float, c_float, c_float, c_void_p, c_void_p],
@@ -421,13 +432,30 @@ def _check_variant(qkv, num_heads, weighting, chunk, head_bias, gate, sinks):
     return WEIGHTINGS[weighting], int(chunk or 0), stride
 
 
+def _check_score_shape(num_heads, softcap, distance):
+    """Two options on the scores that every attention entry point shares: `softcap` c > 0 bounds a score,
+    s <- c tanh(s / c); `distance` (a, b), float32 [num_heads] each, then takes a[h] ln(1 + b[h] (i - j)) off the score of
+    the key that lies i - j positions back.  Returns (cap or 0.0, a, b)."""
+    cap = float(softcap or 0.0)
+    if cap < 0:
+        raise KernelError(f"a score cap of {cap}")
+    if distance is None:
+        return cap, None, None
+    a, b = distance
+    _need(a, torch.float32, "distance[0]", 1); _need(b, torch.float32, "distance[1]", 1)
+    if a.shape[0] != num_heads or b.shape[0] != num_heads:
+        raise KernelError(f"the distance bias has two numbers per query head ({num_heads})")
+    return cap, a, b
+
+
 def paged_attention(qkv, out, k_cache, v_cache, block_table, req_index, positions,
                     num_heads, num_kv_heads, head_dim, scale, window, err, sinks=None,
-                    weighting="softmax", chunk=None, head_bias=None, gate=None):
+                    weighting="softmax", chunk=None, head_bias=None, gate=None, softcap=None, distance=None):
     """out [T, nq*hd] = attention of the q part of qkv over the pages of each token's request.
     `sinks` (float32 [nq]): one more term exp(sinks[h]) in every softmax denominator of head h.
-    `weighting`, `chunk`, `head_bias`, `gate`: see `_check_variant`."""
+    `weighting`, `chunk`, `head_bias`, `gate`: see `_check_variant`.  `softcap`, `distance`: see `_check_score_shape`."""
     _check_sinks(sinks, num_heads)
+    cap, dist_a, dist_b = _check_score_shape(num_heads, softcap, distance)
     mode, chunk, gate_stride = _check_variant(qkv, num_heads, weighting, chunk, head_bias, gate, sinks)
     _need(qkv, None, "qkv", 2); _need(out, qkv.dtype, "out", 2)
     _need(k_cache, qkv.dtype, "k_cache", 4); _need(v_cache, qkv.dtype, "v_cache", 4)
@@ -445,7 +473,7 @@ def paged_attention(qkv, out, k_cache, v_cache, block_table, req_index, position
         _ptr(block_table), block_table.shape[1], _ptr(req_index), _ptr(positions),
         T, num_heads, num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0],
         float(scale), int(window or 0), _ptr(sinks), mode, chunk, _ptr(head_bias), _ptr(gate), gate_stride,
-        _ptr(err), _stream()), "vl_paged_attention")
+        cap, _ptr(dist_a), _ptr(dist_b), _ptr(err), _stream()), "vl_paged_attention")
     return out
 
 
@@ -728,7 +756,7 @@ def silu_mul(gate_up, out, group=0):
 
 ACTIVATIONS = {"silu": 0, "relu": 1, "capped_swish": 2}
 # functions of ONE argument (an expert without a gate: down(f(up h))); the codes continue the gated ones
-UNARY_ACTIVATIONS = {"relu2": 16}           # the square of max(v, 0)
+UNARY_ACTIVATIONS = {"relu2": 16, "tanh": 17}           # the square of max(v, 0); tanh
 
 
 def _act_code(act) -> int:
@@ -835,10 +863,21 @@ def layernorm_rows(x, rows, weight, eps, out):
 
 
 # ---------------------------------------------------------------- latent attention
-def latent_norm_write(proj, q_rank, kv_rank, q_weight, kv_weight, eps, cq_out, slots, cache, err):
+def latent_norm_write(proj, q_rank, kv_rank, q_weight, kv_weight, eps, cq_out, slots, cache, err, rot_dim=0, rotary=None,
+                      positions=None):
     """proj [T, >= q_rank + kv_rank] = [a_q | a_kv]: cq_out [T, q_rank] = rmsnorm(a_q) * q_weight; the cache row
     `slots[t]` of `cache` [pages, 1, page_size, width >= kv_rank] = rmsnorm(a_kv) * kv_weight, zero beyond kv_rank
-    (slots None or negative: no write)."""
+    (slots None or negative: no write).  `rot_dim` > 0: proj carries rot_dim more columns behind a_kv, a key part that is
+    not normed; `rotary` (inv_freq float32 [rot / 2], rot) turns its first rot features by `positions`, and the part is
+    written into the cache row behind the latent."""
+    inv_freq, rot = rotary if rotary is not None else (None, 0)
+    if rot_dim:
+        if rot:
+            _need(inv_freq, torch.float32, "inv_freq", 1); _need(positions, torch.int32, "positions", 1)
+            if inv_freq.shape[0] != rot // 2 or positions.shape[0] != proj.shape[0]:
+                raise KernelError("latent_norm_write: inv_freq holds rot / 2 numbers, positions one per token")
+        if proj.shape[1] < q_rank + kv_rank + rot_dim or (slots is not None and cache.shape[3] < kv_rank + rot_dim):
+            raise KernelError("latent_norm_write: no room for the rotated key part")
     _need(proj, None, "proj", 2); _need(cq_out, proj.dtype, "cq_out", 2)
     _need(q_weight, torch.float32, "q_weight", 1); _need(kv_weight, torch.float32, "kv_weight", 1)
     T = proj.shape[0]
@@ -853,9 +892,61 @@ def latent_norm_write(proj, q_rank, kv_rank, q_weight, kv_weight, eps, cq_out, s
         width, num_slots = cache.shape[3], cache.shape[0] * cache.shape[2]
     _check(_fn("latent", "vl_latent_norm_write")(
         _ptr(proj), dtype_code(proj.dtype), proj.shape[1], T, int(q_rank), int(kv_rank), _ptr(q_weight), _ptr(kv_weight),
-        float(eps), _ptr(cq_out), _ptr(slots), _ptr(cache) if slots is not None else None, width, num_slots,
-        _ptr(err), _stream()), "vl_latent_norm_write")
+        float(eps), _ptr(cq_out), _ptr(slots), _ptr(cache) if slots is not None else None, max(width, kv_rank + rot_dim),
+        num_slots, int(rot_dim), int(rot if rot_dim else 0), _ptr(inv_freq) if rot_dim else None,
+        _ptr(positions) if rot_dim and rot else None, _ptr(err), _stream()), "vl_latent_norm_write")
     return cq_out
+
+
+def rope_heads(x, col0, stride, heads, inv_freq, rot, positions):
+    """In place on x [T, ld]: the features col0 + h * stride + [0, rot) of every head h < heads are turned by the token's
+    position (pairs (i, i + rot/2), angle = position * inv_freq[i] in float32)."""
+    _need(x, None, "x", 2); _need(inv_freq, torch.float32, "inv_freq", 1); _need(positions, torch.int32, "positions", 1)
+    if inv_freq.shape[0] != rot // 2 or positions.shape[0] != x.shape[0]:
+        raise KernelError("rope_heads: inv_freq holds rot / 2 numbers, positions one per token")
+    _check(_fn("latent", "vl_rope_heads")(_ptr(x), dtype_code(x.dtype), x.shape[0], x.shape[1], int(col0), int(stride), int(heads),
+                                          int(rot), _ptr(inv_freq), _ptr(positions), _stream()), "vl_rope_heads")
+    return x
+
+
+def head_norm_write(qkv, positions, slots, q_weight, k_weight, eps, qk_dim, v_norm, v_dim, q_temp, k_cache, v_cache,
+                    num_heads, num_kv_heads, head_dim, err, v_eps=None):
+    """The head work of an attention without rotation, in place on the q part of qkv [T, >= (nq + 2 nkv) hd] and into the
+    cache slots: q and k heads divided by their root mean square over their first `qk_dim` features (0: no norm; weights
+    float32 [hd] or None), the query times 1 + coef ln(floor((pos + 1) / every) + 1) for `q_temp` = (coef, every), every
+    value head divided by its root mean square over `v_dim` features when `v_norm`."""
+    _need(qkv, None, "qkv", 2); _need(positions, torch.int32, "positions", 1)
+    T = qkv.shape[0]
+    for w, n in ((q_weight, "q_weight"), (k_weight, "k_weight")):
+        if w is not None:
+            _need(w, torch.float32, n, 1)
+            if w.shape[0] != head_dim:
+                raise KernelError(f"head_norm_write: {n} has one entry per feature of a head")
+    num_slots, page_size = 0, 1
+    if slots is not None:
+        _need(slots, torch.int32, "slots", 1); _need(k_cache, qkv.dtype, "k_cache", 4); _need(v_cache, qkv.dtype, "v_cache", 4)
+        if k_cache.shape != v_cache.shape or k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim or slots.shape[0] < T:
+            raise KernelError(f"head_norm_write: cache {tuple(k_cache.shape)} does not match {num_kv_heads} heads of {head_dim}")
+        num_slots, page_size = k_cache.shape[0] * k_cache.shape[2], k_cache.shape[2]
+    coef, every = q_temp if q_temp is not None else (0.0, 0)
+    _check(_fn("rope_cache", "vl_head_norm_write")(
+        _ptr(qkv), dtype_code(qkv.dtype), _ptr(positions), _ptr(slots), _ptr(q_weight), _ptr(k_weight), float(eps), int(qk_dim),
+        int(bool(v_norm)), int(v_dim), float(eps if v_eps is None else v_eps), float(coef), int(every),
+        _ptr(k_cache) if slots is not None else None,
+        _ptr(v_cache) if slots is not None else None, T, num_heads, num_kv_heads, head_dim, page_size, num_slots, qkv.shape[1],
+        _ptr(err), _stream()), "vl_head_norm_write")
+    return qkv
+
+
+def sigmoid_gate(x, gate, gate_col=0):
+    """In place: x[t, i] *= sigmoid(gate[t, gate_col + i]) for every column i of x [T, n] (float32 inside)."""
+    _need(x, None, "x", 2); _need(gate, x.dtype, "gate", 2)
+    T, n = x.shape
+    if gate.shape[0] != T or gate_col + n > gate.shape[1]:
+        raise KernelError("sigmoid_gate: the gate's columns leave its rows")
+    _check(_fn("activation", "vl_sigmoid_gate")(_ptr(x), n, _ptr(gate), gate.shape[1], int(gate_col), dtype_code(x.dtype), T, n,
+                                                _stream()), "vl_sigmoid_gate")
+    return x
 
 
 def gemm_heads(a, w, out):
@@ -939,7 +1030,8 @@ def router_slices(K) -> int:
     return 1
 
 
-def moe_route(h, router, top, ids, weights, logits, score="sigmoid", renormalize=False, groups=1, keep_groups=1, bias=None):
+def moe_route(h, router, top, ids, weights, logits, score="sigmoid", renormalize=False, groups=1, keep_groups=1, bias=None,
+              choice_bias=None, group_top=1, renorm_eps=0.0):
     """h [T, K], router [E, K] (float32; or bfloat16 as stored, beside bfloat16 rows: products of two bfloat16 numbers
     are exact in float32, so the tensor cores' float32 sums are the 32-bit logits of the rounded rows):
     logits float32 [router_slices(K), T, E] = partial sums of h router^T; ids int32 [T, top] = the experts with
@@ -947,7 +1039,9 @@ def moe_route(h, router, top, ids, weights, logits, score="sigmoid", renormalize
     `groups` > 1: the experts form that many equal groups of neighbours, a group counts by its largest logit, and only
     experts of the `keep_groups` best groups are chosen from (scores are still taken over all experts).
     `bias` (float32 [E]) is added to the logits before anything else.  "softmax" with `renormalize` is the softmax
-    over the chosen logits alone."""
+    over the chosen logits alone.  `choice_bias` (float32 [E]): experts and groups are chosen by score + choice_bias
+    instead (the weights stay the scores without it); `group_top`: a group counts by the sum of that many of its largest
+    choice values; `renorm_eps` is added to the sum that `renormalize` divides by."""
     _need(h, None, "h", 2); _need(router, None, "router", 2); _need(logits, torch.float32, "logits", 3)
     if router.dtype != torch.float32 and router.dtype != h.dtype:
         raise KernelError("moe_route: the router is float32, or bfloat16 beside bfloat16 rows")
@@ -965,8 +1059,13 @@ def moe_route(h, router, top, ids, weights, logits, score="sigmoid", renormalize
         _need(bias, torch.float32, "bias", 1)
         if bias.shape[0] != E:
             raise KernelError(f"moe_route: the router's bias has {bias.shape[0]} entries for {E} experts")
+    if choice_bias is not None:
+        _need(choice_bias, torch.float32, "choice_bias", 1)
+        if choice_bias.shape[0] != E:
+            raise KernelError(f"moe_route: the choice bias has {choice_bias.shape[0]} entries for {E} experts")
     _check(_fn("moe", "vl_moe_route")(_ptr(logits), slices, T, E, int(top), ROUTER_SCORES[score], int(bool(renormalize)),
-                                      int(groups), int(keep_groups), _ptr(bias), _ptr(ids), _ptr(weights), _stream()),
+                                      int(groups), int(keep_groups), _ptr(bias), _ptr(choice_bias), int(group_top),
+                                      float(renorm_eps), _ptr(ids), _ptr(weights), _stream()),
            "vl_moe_route")
 
 
@@ -1358,6 +1457,43 @@ def delta_scan(qkv, decay, decay_col, dt_bias, A_log, proj, beta_col, q_scale, u
                                              dtype_code(proj.dtype), proj.shape[1], beta_col, float(q_scale), float(unit_eps),
                                              sp, stride, _ptr(cu), _ptr(slots), B, _ptr(o), H, G, D, P, _stream()),
            "vl_delta_scan")
+    return o
+
+
+def token_shift_multi(h, mu, state, state_off, cu, slots, req_index, positions, out):
+    """out[s, t] = h[t] + (h[t - 1] - h[t]) * mu[s]: S mixes at once, h [T, W] and out [S, T, W] in one dtype, mu float32
+    [S, W]; the row before a portion's first token is state[slot, state_off : state_off + W] (float32), which the launch
+    replaces by the portion's last row."""
+    _need(h, None, "h", 2); _need(mu, torch.float32, "mu", 2); _need(out, h.dtype, "out", 3)
+    T, W = h.shape
+    S = mu.shape[0]
+    if mu.shape[1] != W or out.shape != (S, T, W) or req_index.shape[0] != T or positions.shape[0] != T:
+        raise KernelError("token_shift_multi: shapes disagree")
+    base, stride = _state_args(state, state_off, W)
+    _seg_args(cu, slots)
+    _need(req_index, torch.int32, "req_index", 1); _need(positions, torch.int32, "positions", 1)
+    _check(_fn("recurrent", "vl_token_shift_multi")(_ptr(h), _ptr(mu), S, base, stride, _ptr(cu), _ptr(slots), _ptr(req_index),
+                                                    _ptr(positions), _ptr(out), dtype_code(h.dtype), T, W, _stream()),
+           "vl_token_shift_multi")
+    return out
+
+
+def decay_scan(r, k, v, z, w0, u, state, state_off, cu, slots, o, H, D, P):
+    """Per head a memory S [D, P] with a decay per key channel: o_t = (S + diag(u) k_t v_t^T)^T r_t, then
+    S <- diag(exp(-exp(z_t + w0))) S + k_t v_t^T.  r, k, z: (tensor [T, ld], first column) with H*D columns, v likewise
+    with H*P, all of one dtype; w0, u float32 [H*D]; o float32 [T, H*P]; the state as `scan_state_floats(H, D, P)`."""
+    (rt, rc), (kt, kc), (vt, vc), (zt, zc) = r, k, v, z
+    for t, n in ((rt, "r"), (kt, "k"), (vt, "v"), (zt, "z")):
+        _need(t, rt.dtype, n, 2)
+    _need(o, torch.float32, "o", 2); _need(w0, torch.float32, "w0", 1); _need(u, torch.float32, "u", 1)
+    T = rt.shape[0]
+    if kt.shape[0] != T or vt.shape[0] != T or zt.shape[0] != T or o.shape != (T, H * P) or w0.shape[0] != H * D or u.shape[0] != H * D:
+        raise KernelError("decay_scan: shapes disagree")
+    B = _seg_args(cu, slots)
+    sp, stride = _state_args(state, state_off, scan_state_floats(H, D, P))
+    _check(_fn("recurrent", "vl_decay_scan")(_ptr(rt), rt.shape[1], int(rc), _ptr(kt), kt.shape[1], int(kc), _ptr(vt), vt.shape[1],
+                                             int(vc), _ptr(zt), zt.shape[1], int(zc), dtype_code(rt.dtype), _ptr(w0), _ptr(u), sp,
+                                             stride, _ptr(cu), _ptr(slots), B, _ptr(o), H, D, P, _stream()), "vl_decay_scan")
     return o
 
 

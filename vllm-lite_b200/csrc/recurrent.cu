@@ -722,3 +722,160 @@ extern "C" int vl_gate_norm(const float* y, const void* gate, int dtype, int ld,
     }
     return VL_ERR_UNSUPPORTED;
 }
+
+// ------------------------------------------------------------------------------------------ several token shifts at once
+// out[s][t] = h[t] + (h[t - 1] - h[t]) * mu[s], s < S: S mixes of a row with the row of the token before, each with its own
+// mu [W] (float32 arithmetic; h and out in the activation dtype, out [S, T, W]).  The row before a portion's first token
+// is the state's row (float32; zeros in a fresh slot), which the block of that token replaces by the portion's last row,
+// as in vl_token_shift.  A row at a negative position passes unchanged into every mix and touches no state.
+template <typename T>
+__global__ void __launch_bounds__(256)
+token_shift_multi_kernel(const T* __restrict__ h, const float* __restrict__ mu, int S, float* state, long long state_stride,
+                         const int* __restrict__ cu, const int* __restrict__ slots, const int* __restrict__ req_index,
+                         const int* __restrict__ positions, T* __restrict__ out, int ntok, int W) {
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int b = req_index[t], pos = positions[t];
+    const bool live = pos >= 0;
+    const int first = live ? cu[b] : 0, last = live ? cu[b + 1] - 1 : 0;
+    pdl_wait();
+    const T* xr = h + (size_t)t * W;
+    const bool head = live && t == first;
+    float* st = live ? state + (long long)slots[b] * state_stride : nullptr;
+    const T* keep = h + (size_t)last * W;
+    for (int i = threadIdx.x; i < W; i += 256) {
+        const float v = to_f32(xr[i]);
+        float p = v;
+        if (live) {
+            if (head) { p = st[i]; st[i] = to_f32(keep[i]); }
+            else p = to_f32(xr[i - W]);
+        }
+        for (int s = 0; s < S; ++s)
+            out[((size_t)s * ntok + t) * W + i] = from_f32<T>(v + (p - v) * mu[(size_t)s * W + i]);
+    }
+}
+
+extern "C" int vl_token_shift_multi(const void* h, const float* mu, int S, float* state, long long state_stride, const int* cu,
+                                    const int* slots, const int* req_index, const int* positions, void* out, int dtype, int T,
+                                    int W, void* stream) {
+    if (T <= 0) return VL_OK;
+    if (W <= 0 || S <= 0 || state_stride < W) return VL_ERR_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VL_F32)
+        return vl_launch(token_shift_multi_kernel<float>, dim3(T), dim3(256), 0, s, (const float*)h, mu, S, state, state_stride, cu,
+                         slots, req_index, positions, (float*)out, T, W);
+    if (dtype == VL_BF16)
+        return vl_launch(token_shift_multi_kernel<bf16>, dim3(T), dim3(256), 0, s, (const bf16*)h, mu, S, state, state_stride, cu,
+                         slots, req_index, positions, (bf16*)out, T, W);
+    return VL_ERR_UNSUPPORTED;
+}
+
+// ------------------------------------------------------------------------------------------ memory with a decay per key channel
+// Per head, S [D x P] from the request's state:   o_t = (S + diag(u) k_t v_t^T)^T r_t;   S <- diag(w_t) S + k_t v_t^T
+// with w_t = exp(-exp(z_t + w0)) per key channel (z the raw decay, w0 [H*D]) and u [H*D] a bonus for the current token alone.
+// r, k, z float32 rows with H*D columns from `rc`, `kc`, `zc` on; v float32 with H*P columns.  o float32 [T, H*P].
+// Staged per token: r [D] | k [D] | decay [D] | v [CT]; the two exponentials are taken once per token on the staged values.
+template <typename TP, int ROWS, int L>
+__global__ void __launch_bounds__(RC_MAX_THREADS)
+decay_scan_kernel(const TP* __restrict__ rp, int ldr, int rc, const TP* __restrict__ kp, int ldk, int kc, const TP* __restrict__ vp,
+                  int ldv, int vc, const TP* __restrict__ zp, int ldz, int zc, const float* __restrict__ w0,
+                  const float* __restrict__ u, float* __restrict__ state, long long state_stride, const int* __restrict__ cu,
+                  const int* __restrict__ slots, float* __restrict__ o, int H, int D, int P, int chunk) {
+    extern __shared__ float sm[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int s0 = cu[b], n = cu[b + 1] - s0;
+    if (n <= 0) return;
+    const int NT = blockDim.x, CT = NT / L, tid = threadIdx.x;
+    const int col = tid / L, l = tid % L;
+    const int p0 = blockIdx.z * CT, p = p0 + col;
+    const bool live = p < P;
+    const int VEC = 3 * D + CT;
+    float* S = scan_state<ROWS>(state, state_stride, slots[b], h);
+    float s[ROWS], ub[ROWS];
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i) {
+        s[i] = S[(size_t)i * NT];
+        const int r = l + L * i;
+        ub[i] = r < D ? u[(size_t)h * D + r] : 0.f;
+    }
+    auto raw = [&](int row, int e) -> float {
+        const size_t t = (size_t)(s0 + row);
+        if (e < D) return to_f32(rp[t * ldr + rc + (size_t)h * D + e]);
+        if (e < 2 * D) return to_f32(kp[t * ldk + kc + (size_t)h * D + (e - D)]);
+        if (e < 3 * D) return to_f32(zp[t * ldz + zc + (size_t)h * D + (e - 2 * D)]);
+        return p0 + (e - 3 * D) < P ? to_f32(vp[t * ldv + vc + (size_t)h * P + p0 + (e - 3 * D)]) : 0.f;
+    };
+    auto finish = [&](float* buf, int m) {
+        for (int idx = tid; idx < m * D; idx += NT) {
+            const int k = idx / D, r = idx - k * D;
+            float* v = buf + (size_t)k * VEC + 2 * D + r;
+            *v = expf(-expf(*v + w0[(size_t)h * D + r]));
+        }
+    };
+    float pf[RC_PREFETCH];
+    int m = min(chunk, n);
+    scan_prefetch(pf, 0, m, VEC, raw);
+    scan_commit(pf, sm, m, VEC);
+    __syncthreads();
+    finish(sm, m);
+    __syncthreads();
+    int cur = 0;
+    for (int t0 = 0; t0 < n; t0 += chunk) {
+        const int mn = min(chunk, n - t0 - m);
+        if (mn > 0) scan_prefetch(pf, t0 + m, mn, VEC, raw);
+        const float* buf = sm + (size_t)cur * chunk * VEC;
+        for (int k = 0; k < m; ++k) {
+            const float* v = buf + (size_t)k * VEC;
+            const float vj = v[3 * D + col];
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < ROWS; ++i) {
+                const int r = l + L * i;
+                if (r < D) {
+                    const float kv = v[D + r] * vj;
+                    acc += v[r] * (s[i] + ub[i] * kv);
+                    s[i] = v[2 * D + r] * s[i] + kv;
+                }
+            }
+            acc = group_sum<L>(acc);
+            if (live && l == 0) o[(size_t)(s0 + t0 + k) * H * P + (size_t)h * P + p] = acc;
+        }
+        if (mn > 0) {
+            float* nxt = sm + (size_t)(cur ^ 1) * chunk * VEC;
+            scan_commit(pf, nxt, mn, VEC);
+            __syncthreads();
+            finish(nxt, mn);
+        }
+        __syncthreads();
+        cur ^= 1;
+        m = mn;
+    }
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i) S[(size_t)i * NT] = s[i];
+}
+
+extern "C" int vl_decay_scan(const void* rp, int ldr, int rc, const void* kp, int ldk, int kc, const void* vp, int ldv, int vc,
+                             const void* zp, int ldz, int zc, int dtype, const float* w0, const float* u, float* state,
+                             long long state_stride, const int* cu, const int* slots, int B, float* o, int H, int D, int P,
+                             void* stream) {
+    if (B <= 0) return VL_OK;
+    if (H <= 0 || D <= 0 || P <= 0 || rc < 0 || kc < 0 || vc < 0 || zc < 0 || rc + H * D > ldr || kc + H * D > ldk ||
+        vc + H * P > ldv || zc + H * D > ldz)
+        return VL_ERR_ARGUMENT;
+    ScanShape sh;
+    if (!scan_shape(D, P, &sh)) return VL_ERR_UNSUPPORTED;
+    const int CT = sh.CT, VEC = 3 * D + CT, chunk = scan_chunk(VEC, sh.threads);
+    if (!chunk) return VL_ERR_UNSUPPORTED;
+    dim3 grid(H, B, sh.Z);
+    const size_t smem = sizeof(float) * (size_t)2 * chunk * VEC;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VL_F32)
+        SCAN_LAUNCH(decay_scan_kernel, float, sh, grid, smem, s, (const float*)rp, ldr, rc, (const float*)kp, ldk, kc,
+                    (const float*)vp, ldv, vc, (const float*)zp, ldz, zc, w0, u, state, state_stride, cu, slots, o, H, D, P, chunk);
+    if (dtype == VL_BF16)
+        SCAN_LAUNCH(decay_scan_kernel, bf16, sh, grid, smem, s, (const bf16*)rp, ldr, rc, (const bf16*)kp, ldk, kc,
+                    (const bf16*)vp, ldv, vc, (const bf16*)zp, ldz, zc, w0, u, state, state_stride, cu, slots, o, H, D, P, chunk);
+    return VL_ERR_UNSUPPORTED;
+}

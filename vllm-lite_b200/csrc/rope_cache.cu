@@ -465,3 +465,85 @@ extern "C" int vl_conv_rows_norm_rope_write(const void* proj, int pld, const flo
 #undef CONV_ROWS_LAUNCH
     return VL_ERR_UNSUPPORTED;
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Head work of an attention without rotation: every head of q and k divided by its root mean square
+// (a weight per feature, or none), the query then multiplied by a factor that grows with its position,
+//     q <- q (1 + temp_coef ln(floor((pos + 1) / temp_every) + 1))          (temp_every <= 0: no factor),
+// every value head divided by its own root mean square when `v_norm` (no weight), k and v written to the token's
+// cache slot.  Heads lie in rows as [q (nq) | k (nkv) | v (nkv)], each `hd` features wide; the means run over
+// the first `qk_dim` / `v_dim` features (what lies behind them in a padded head is zero and stays zero).
+// A warp per (token, head), the head in registers; sums and factors in float32.  hd up to ROPE_MAX_HD.
+// ---------------------------------------------------------------------------------------------------------
+#define HEADNORM_PER_LANE (ROPE_MAX_HD / 32)
+template <typename T>
+__global__ void __launch_bounds__(ROPE_THREADS)
+head_norm_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ slots,
+                       const float* __restrict__ qw, const float* __restrict__ kw, float eps, int qk_dim, int v_norm,
+                       int v_dim, float v_eps, float temp_coef, int temp_every, T* __restrict__ kcache, T* __restrict__ vcache,
+                       int nq, int nkv, int hd, int page_size, long long num_slots, int row_stride, unsigned* err) {
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.y * (ROPE_THREADS / 32) + warp;
+    if (head >= nq + 2 * nkv) return;
+    const int pos = positions[t];
+    const int slot = slots ? slots[t] : -1;
+    pdl_wait();
+    const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
+    T* src = qkv + (size_t)t * row_stride + (size_t)head * hd;
+    T* dst = src;
+    if (!is_q) {
+        if (slot < 0) return;
+        if ((long long)slot >= num_slots) {
+            if (lane == 0 && head == nq) atomicOr(err, VL_DEV_BAD_SLOT);
+            return;
+        }
+        const int page = slot / page_size, off = slot - page * page_size;
+        const int kvh = is_k ? head - nq : head - nq - nkv;
+        dst = (is_k ? kcache : vcache) + (((size_t)page * nkv + kvh) * page_size + off) * hd;
+    }
+    float v[HEADNORM_PER_LANE];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < HEADNORM_PER_LANE; ++k) {
+        const int i = lane + 32 * k;
+        v[k] = i < hd ? to_f32(src[i]) : 0.f;
+        ss += v[k] * v[k];
+    }
+    float f = 1.f;
+    const bool normed = is_q || is_k ? qk_dim > 0 : v_norm != 0;
+    if (normed) {                                                     // (warp-uniform)
+        ss = warp_sum(ss);
+        f = 1.0f / sqrtf(ss / (float)(is_q || is_k ? qk_dim : v_dim) + (is_q || is_k ? eps : v_eps));
+    }
+    if (is_q && temp_every > 0 && pos >= 0) f *= 1.0f + temp_coef * logf((float)((pos + 1) / temp_every + 1));
+    const float* w = is_q ? qw : (is_k ? kw : nullptr);
+#pragma unroll
+    for (int k = 0; k < HEADNORM_PER_LANE; ++k) {
+        const int i = lane + 32 * k;
+        if (i < hd) dst[i] = from_f32<T>(w ? v[k] * f * w[i] : v[k] * f);
+    }
+}
+
+extern "C" int vl_head_norm_write(void* qkv, int dtype, const int* positions, const int* slots, const float* qw, const float* kw,
+                                  float eps, int qk_dim, int v_norm, int v_dim, float v_eps, float temp_coef, int temp_every, void* kcache,
+                                  void* vcache, int T, int nq, int nkv, int hd, int page_size, long long num_slots,
+                                  int row_stride, unsigned* err, void* stream) {
+    if (T <= 0) return VL_OK;
+    if (nq <= 0 || nkv <= 0 || hd <= 0 || hd > ROPE_MAX_HD) return VL_ERR_UNSUPPORTED;
+    if (qk_dim < 0 || qk_dim > hd || v_dim <= 0 || v_dim > hd || row_stride < (nq + 2 * nkv) * hd || page_size <= 0)
+        return VL_ERR_ARGUMENT;
+    const int nheads = nq + 2 * nkv, per = ROPE_THREADS / 32;
+    dim3 grid(T, (nheads + per - 1) / per);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VL_F32)
+        return vl_launch(head_norm_write_kernel<float>, grid, dim3(ROPE_THREADS), 0, s, (float*)qkv, positions, slots, qw, kw, eps,
+                         qk_dim, v_norm, v_dim, v_eps, temp_coef, temp_every, (float*)kcache, (float*)vcache, nq, nkv, hd, page_size,
+                         num_slots, row_stride, err);
+    if (dtype == VL_BF16)
+        return vl_launch(head_norm_write_kernel<bf16>, grid, dim3(ROPE_THREADS), 0, s, (bf16*)qkv, positions, slots, qw, kw, eps,
+                         qk_dim, v_norm, v_dim, v_eps, temp_coef, temp_every, (bf16*)kcache, (bf16*)vcache, nq, nkv, hd, page_size,
+                         num_slots, row_stride, err);
+    return VL_ERR_UNSUPPORTED;
+}

@@ -69,6 +69,11 @@ class GqaAttention:
             d.update({qb: TensorDecl((qd,)), kb: TensorDecl((kd,)), vb: TensorDecl((vdim,))})
         if spec.out_bias:
             d[ob] = TensorDecl((spec.hidden_size,))
+        if spec.distance_bias is not None:
+            d.update({spec.distance_bias[0]: TensorDecl((spec.num_heads,), init="unit"),
+                      spec.distance_bias[1]: TensorDecl((spec.num_heads,), init="rate")})
+        if spec.gate is not None:
+            d[spec.gate] = TensorDecl((spec.num_heads * vd, spec.hidden_size))
         if spec.qk_norm is not None:
             for side in spec.norm_prefixes:
                 for name, decl in NORMS.get(spec.qk_norm.kind).declare(spec.qk_norm).items():
@@ -93,6 +98,14 @@ class GqaAttention:
         import dataclasses
         hd, vd, pd = spec.head_dim, spec.v_head_dim or spec.head_dim, self.padded_head_dim(spec)
         self.true_spec = spec
+        # an attention with options on its scores or around them runs its own sequence of kernels (`_call_with_options`);
+        # with a query factor or a value norm the head work is a kernel of its own, which knows the heads' true sizes
+        self.own_head_work = spec.q_temp is not None or spec.v_norm is not None
+        self.with_options = bool(self.own_head_work or spec.softcap or spec.distance_bias is not None or spec.unit_sink
+                                 or spec.gate is not None)
+        if self.own_head_work and (spec.position is not None or spec.bias or
+                                   (spec.qk_norm is not None and spec.qk_norm.kind != "rms_norm")):
+            raise ValueError("a query factor or a value norm goes with RMS head norms, no rotation and no projection bias")
         # what the kernels see: heads of the padded size (scale and window as given)
         spec = dataclasses.replace(spec, head_dim=pd, v_head_dim=None,
                                    scale=spec.scale if spec.scale is not None else hd ** -0.5,
@@ -120,14 +133,34 @@ class GqaAttention:
         if biases is not None:
             bias = torch.cat([_pad_heads(biases[0], nq, hd, pd), _pad_heads(biases[1], nkv, hd, pd),
                               _pad_heads(biases[2], nkv, vd, pd)], dim=0)
-        self.qkv_proj = Linear(torch.cat([wq, wk, wv], dim=0).contiguous(), bias)
+        stacked = [wq, wk, wv]
+        self.gate_col = None
+        if spec.gate is not None:
+            # the gate's rows follow the value heads' padding; sigmoid(0) times a padded zero stays zero
+            stacked.append(_pad_heads(weights[spec.gate], nq, vd, pd))
+            self.gate_col = (nq + 2 * nkv) * pd
+            if bias is not None:
+                bias = torch.cat([bias, torch.zeros(nq * pd, dtype=bias.dtype, device=bias.device)], dim=0)
+        self.qkv_proj = Linear(torch.cat(stacked, dim=0).contiguous(), bias)
+        f32 = lambda t: t.to(device=ctx.device, dtype=torch.float32).contiguous()
+        self.distance = None
+        if spec.distance_bias is not None:
+            self.distance = (f32(weights[spec.distance_bias[0]]), f32(weights[spec.distance_bias[1]]))
+        self.sinks = torch.zeros(nq, dtype=torch.float32, device=ctx.device) if spec.unit_sink else None
         self.o_proj = Linear(wo.contiguous(), weights[spec.bias_names[3]].float() if spec.out_bias else None)
         self.q_norm = self.k_norm = None
         # The kernel that rotates and writes the cache also applies an RMS norm to every head.  A head norm
         # that says it is one (`fused_rms()` -> (weight, eps)) runs there; any other kind must change the
         # heads itself (`apply_heads`), and the kernel is then given no norm.
         self.fused_head_norm = None
-        if spec.qk_norm is not None:
+        self.head_weights = (None, None)
+        if spec.qk_norm is not None and self.own_head_work:
+            # the head-work kernel divides by the mean over the true size itself: weights are padded, nothing else
+            if spec.qk_norm.has_weight:
+                tn = self.true_spec.qk_norm
+                self.head_weights = tuple(_pad_heads(f32(sub_weights(weights, side)[tn.tensor]) + float(tn.offset), 1, hd, pd)
+                                          for side in spec.norm_prefixes)
+        elif spec.qk_norm is not None:
             cls = NORMS.get(spec.qk_norm.kind)
             true_norm = self.true_spec.qk_norm
             norms = []
@@ -160,10 +193,44 @@ class GqaAttention:
 
     def factors_norms(self, M) -> bool:
         """For M rows: the input may come as `ScaledRows` and the result may go `into_stream`."""
-        return self.qkv_proj.factors_norms(M) and self.o_proj.factors_norms(M)
+        return not self.with_options and self.qkv_proj.factors_norms(M) and self.o_proj.factors_norms(M)
+
+    def _call_with_options(self, h, step, cache):
+        """project (q | k | v | gate) -> head work -> attention with the score options -> output gate -> output projection."""
+        from ..csrc import ops
+        from . import attention_dispatch
+        s, ts = self.spec, self.true_spec
+        group = step.groups[cache.group]
+        qkv = self.qkv_proj(h, step, "attn.qkv")
+        slots = group.slots if cache.writes else None
+        if self.own_head_work:
+            qk = ts.qk_norm
+            ops.head_norm_write(qkv, step.positions, slots, self.head_weights[0], self.head_weights[1],
+                                qk.eps if qk is not None else 0.0, ts.head_dim if qk is not None else 0,
+                                ts.v_norm is not None, ts.v_head_dim or ts.head_dim, ts.q_temp, cache.k, cache.v,
+                                s.num_heads, s.num_kv_heads, s.head_dim, step.err, v_eps=ts.v_norm)
+        else:
+            fused = self.position.fused_rotary() if self.position is not None else None
+            if self.position is not None and fused is None:
+                self.position.apply(qkv, step.positions, s.num_heads, s.num_kv_heads, s.head_dim, step)
+            inv_freq, rot = fused if fused is not None else (None, 0)
+            if self.q_norm is not None and self.fused_head_norm is None:
+                self.q_norm.apply_heads(qkv, 0, s.num_heads, s.head_dim, step)
+                self.k_norm.apply_heads(qkv, s.num_heads, s.num_kv_heads, s.head_dim, step)
+            qw, kw, eps = self.fused_head_norm if self.fused_head_norm is not None else (None, None, 0.0)
+            ops.qk_norm_rope_write(qkv, step.positions, slots, qw, kw, eps, inv_freq, rot, cache.k, cache.v,
+                                   s.num_heads, s.num_kv_heads, s.head_dim, step.err)
+        out = step.workspace.get(step.tag + "attn.out", (qkv.shape[0], s.num_heads * s.head_dim), self.dtype)
+        attention_dispatch.run(qkv, out, cache, group, step, s, self.scale, sinks=self.sinks, softcap=ts.softcap,
+                               distance=self.distance)
+        if self.gate_col is not None:
+            ops.sigmoid_gate(out, qkv, self.gate_col)
+        return self.o_proj(out, step, "attn.o")
 
     def __call__(self, h, step, cache, sink=None):
         from ..csrc import ops
+        if self.with_options:
+            return self._call_with_options(h, step, cache)
         s = self.spec
         group = step.groups[cache.group]
         qkv = self.qkv_proj(h, step, "attn.qkv")

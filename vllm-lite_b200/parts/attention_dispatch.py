@@ -70,15 +70,20 @@ def _variant_decode_ok(ops, spec, num_tokens, max_context, mask_chunk) -> bool:
 
 
 def run(qkv, out, cache, group, step, spec, scale, fold=None, sinks=None, weighting="softmax", chunk=None,
-        head_bias=None, gate=None):
+        head_bias=None, gate=None, softcap=None, distance=None):
     """`spec`: anything with num_heads, num_kv_heads, head_dim and window.
     `fold` (only where `folds_head_work` said so): (q_weight, k_weight, eps, inv_freq, rotary_dim, slots) of the
     head work that the mixer left undone.
     `sinks` (float32 [num_heads]): a number per head that joins every softmax denominator as exp(sink).
     `weighting` "sigmoid" (with `head_bias`, float32 [num_heads]): a key weighs sigmoid(score + head_bias[h]) by
     itself; `chunk`: positions in blocks of that many, no key of an earlier block is read; `gate` [T, >= num_heads]:
-    head h's output is multiplied by sigmoid(gate[t, h])."""
+    head h's output is multiplied by sigmoid(gate[t, h]).
+    `softcap` c: score <- c tanh(score / c); `distance` (a, b), float32 [num_heads] each: a[h] ln(1 + b[h] (i - j)) is
+    taken off the score of the key j that query i reads."""
     from ..csrc import ops
+    if softcap or distance is not None:
+        return _run_shaped(ops, qkv, out, cache, group, step, spec, scale, sinks, weighting, chunk, head_bias, gate,
+                           softcap, distance)
     if weighting != "softmax" or chunk is not None or head_bias is not None or gate is not None:
         return _run_variant(ops, qkv, out, cache, group, step, spec, scale, weighting, chunk, head_bias, gate, sinks)
     if fold is not None and not folds_head_work(qkv.dtype, step, spec, group, qkv.shape[0]):
@@ -129,3 +134,11 @@ def _run_variant(ops, q, out, cache, group, step, spec, scale, weighting, chunk,
     return ops.paged_attention(q, out, cache.k, cache.v, group.block_table, step.req_index, step.positions,
                                spec.num_heads, spec.num_kv_heads, spec.head_dim, scale, spec.window, step.err, sinks=sinks,
                                weighting=weighting, chunk=chunk, head_bias=head_bias, gate=gate)
+
+
+def _run_shaped(ops, q, out, cache, group, step, spec, scale, sinks, weighting, chunk, head_bias, gate, softcap, distance):
+    """Attention whose scores are capped or lose a bias that grows with the distance."""
+    return ops.paged_attention(q, out, cache.k, cache.v, group.block_table, step.req_index, step.positions,
+                               spec.num_heads, spec.num_kv_heads, spec.head_dim, scale, spec.window, step.err, sinks=sinks,
+                               weighting=weighting, chunk=chunk, head_bias=head_bias, gate=gate, softcap=softcap,
+                               distance=distance)

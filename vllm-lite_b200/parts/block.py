@@ -154,6 +154,66 @@ class PostNormBlock:
             residual.cast = self.norm2.add_normed(y, residual.x, step, buf, **kw)
 
 
+@BLOCKS.register("sandwich")
+class SandwichBlock:
+    """x += post1(mixer(norm1(x))); x += post2(ffn(norm2(x))): every sub-layer between a norm on its input and a norm on
+    its output.  The input norms read the float32 stream through their own kernel; the output norms add their result into
+    it (`add_normed`).  A block without a feed-forward (`spec.ffn` None) is its first half alone."""
+
+    @staticmethod
+    def declare(spec: BlockSpec) -> dict:
+        norm1, mixer, norm2, ffn = spec.names
+        post1, post2 = spec.post_names
+        d = {}
+        d.update(prefixed(NORMS.get(spec.norm1.kind).declare(spec.norm1), norm1))
+        d.update(prefixed(MIXERS.get(spec.mixer.kind).declare(spec.mixer), mixer))
+        d.update(prefixed(NORMS.get(spec.post_norms[0].kind).declare(spec.post_norms[0]), post1))
+        if spec.ffn is not None:
+            d.update(prefixed(NORMS.get(spec.norm2.kind).declare(spec.norm2), norm2))
+            d.update(prefixed(FEED_FORWARDS.get(spec.ffn.kind).declare(spec.ffn), ffn))
+            d.update(prefixed(NORMS.get(spec.post_norms[1].kind).declare(spec.post_norms[1]), post2))
+        return d
+
+    @staticmethod
+    def cache_need(spec: BlockSpec):
+        return MIXERS.get(spec.mixer.kind).cache_need(spec.mixer)
+
+    def __init__(self, spec: BlockSpec, weights: dict, ctx):
+        if spec.post_norms is None:
+            raise ValueError("a sandwich block names the two norms on its sub-layers' outputs (post_norms)")
+        self.spec = spec
+        self.dtype = ctx.dtype
+        norm1, mixer, norm2, ffn = spec.names
+        post1, post2 = spec.post_names
+        self.norm1 = NORMS.get(spec.norm1.kind)(spec.norm1, _exact(weights, norm1, spec.norm1), ctx)
+        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, sub_weights(weights, mixer), ctx)
+        self.post1 = NORMS.get(spec.post_norms[0].kind)(spec.post_norms[0], _exact(weights, post1, spec.post_norms[0]), ctx)
+        self.norm2 = self.ffn = self.post2 = None
+        if spec.ffn is not None:
+            self.norm2 = NORMS.get(spec.norm2.kind)(spec.norm2, _exact(weights, norm2, spec.norm2), ctx)
+            self.ffn = FEED_FORWARDS.get(spec.ffn.kind)(spec.ffn, sub_weights(weights, ffn), ctx)
+            self.post2 = NORMS.get(spec.post_norms[1].kind)(spec.post_norms[1], _exact(weights, post2, spec.post_norms[1]), ctx)
+        for norm in (self.post1, self.post2):
+            if norm is not None and not hasattr(norm, "add_normed"):
+                raise TypeError(f"norm kind {norm.spec.kind!r} cannot norm a sub-layer's output into the stream: "
+                                f"it offers no add_normed(y, x, step, cast)")
+        self.graph_safe = bool(getattr(self.mixer, "graph_safe", False)
+                               and (self.ffn is None or getattr(self.ffn, "graph_safe", False)))
+
+    def __call__(self, residual, step, cache):
+        if residual.normed is not None:
+            raise NotImplementedError("a sandwich block after a block that leaves a norm's output in factored form")
+        h = self.norm1(residual.x, residual.pending, step, tag="norm1")
+        residual.pending = None
+        residual.cast = None
+        y = self.mixer(h, step, cache)
+        self.post1.add_normed(y, residual.x, step, None)
+        if self.ffn is not None:
+            h = self.norm2(residual.x, None, step, tag="norm2")
+            y = self.ffn(h, step)
+            self.post2.add_normed(y, residual.x, step, None)
+
+
 def _exact(weights, prefix, norm_spec):
     """The tensors of a norm whose prefix may be its weight's whole name (`tensor` == "")."""
     if getattr(norm_spec, "tensor", "weight") == "":

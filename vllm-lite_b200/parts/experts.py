@@ -18,11 +18,16 @@ In bfloat16 (sizes permitting) the first product does the work of its neighbours
 rows through the sorted index (no sorted copy), applies the expert weight to its float32 sums
 (W (s h) = s (W h)) and the activation to its own tile (gate and up rows interleaved in blocks of 8), so
 the step is router, sort, two products and the sum: five launches instead of seven.
+
+Options of the router (`ops.moe_route`): a bias on the logits, a bias on the scores that only the choice sees, groups of
+neighbouring experts that count by their largest or by the sum of their largest choice values, renormalised weights.
+A `shared` feed-forward (any registered kind) runs for every token beside the experts and is added to their sum.
 """
 from __future__ import annotations
 
 import torch
 
+from .base import prefixed, sub_weights
 from .registry import FEED_FORWARDS
 from .spec import RoutedExpertsSpec, TensorDecl
 
@@ -40,6 +45,10 @@ class RoutedExperts:
         d = {spec.router: TensorDecl((spec.num_experts, H))}
         if spec.router_bias is not None:
             d[spec.router + spec.router_bias] = TensorDecl((spec.num_experts,))
+        if spec.choice_bias is not None:
+            d[spec.choice_bias] = TensorDecl((spec.num_experts,), init="unit")
+        if spec.shared is not None:
+            d.update(prefixed(FEED_FORWARDS.get(spec.shared.kind).declare(spec.shared), spec.shared_prefix))
         for e in range(spec.num_experts):
             p = spec.expert_prefix.format(e)
             d.update({p + up: TensorDecl((I, H)), p + down: TensorDecl((H, I))})
@@ -73,6 +82,16 @@ class RoutedExperts:
         self.router_bias = None
         if spec.router_bias is not None:
             self.router_bias = weights[spec.router + spec.router_bias].to(device=ctx.device, dtype=torch.float32).contiguous()
+        self.choice_bias = None
+        if spec.choice_bias is not None:
+            self.choice_bias = weights[spec.choice_bias].to(device=ctx.device, dtype=torch.float32).contiguous()
+        if spec.group_top < 1 or spec.renorm_eps < 0:
+            raise ValueError(f"routed experts: group_top {spec.group_top}, renorm_eps {spec.renorm_eps}")
+        # one more feed-forward that every token passes, added to the experts' sum
+        self.shared = None
+        if spec.shared is not None:
+            self.shared = FEED_FORWARDS.get(spec.shared.kind)(spec.shared, sub_weights(weights, spec.shared_prefix), ctx)
+            self.graph_safe = bool(getattr(self.shared, "graph_safe", False))
         I, H = spec.intermediate_size, spec.hidden_size
         # columns of the first product: gate and up rows, or the up rows alone
         self.first_n = 2 * I if spec.gated else I
@@ -105,7 +124,7 @@ class RoutedExperts:
         place = ws.get(tag + "moe.place", (pairs,), torch.int32)
         logits = ws.get(tag + "moe.logits", (ops.router_slices(H), T, E), torch.float32)
         ops.moe_route(h, self.router, top, ids, weights, logits, s.score, s.renormalize, s.groups, s.keep_groups,
-                      bias=self.router_bias)
+                      bias=self.router_bias, choice_bias=self.choice_bias, group_top=s.group_top, renorm_eps=s.renorm_eps)
         ops.moe_align(ids, E, bm, sorted_rows, tile_group, place)
         act = ws.get(tag + "moe.act", (cap, I), self.dtype)
         if big:
@@ -114,7 +133,8 @@ class RoutedExperts:
             ops.gemm_grouped_tc5(rows, self.gate_up, act, tile_group, step.err, sorted_rows,
                                  weights if s.scale_input else None, s.activation, s.alpha, s.limit, s.up_shift)
             res = ops.gemm_grouped_tc5(act, self.down, ws.get(tag + "moe.down", (cap, H), self.dtype), tile_group, step.err)
-            return ops.moe_combine(res, place, weights, top, ws.get(tag + "moe.out", (T, H), self.dtype), not s.scale_input)
+            out = ops.moe_combine(res, place, weights, top, ws.get(tag + "moe.out", (T, H), self.dtype), not s.scale_input)
+            return self._add_shared(out, h, step)
         if self.fused:
             ops.gemm_grouped_fused(h, self.gate_up, act, tile_group, bm, sorted_rows, top,
                                    weights if s.scale_input else None, s.activation, s.alpha, s.limit, s.up_shift)
@@ -127,4 +147,10 @@ class RoutedExperts:
                 ops.unary_act(gu, act, s.activation)
         res = ops.gemm_grouped(act, self.down, ws.get(tag + "moe.down", (cap, H), self.dtype), tile_group, bm)
         out = ws.get(tag + "moe.out", (T, H), self.dtype)
-        return ops.moe_combine(res, place, weights, top, out, not s.scale_input)
+        return self._add_shared(ops.moe_combine(res, place, weights, top, out, not s.scale_input), h, step)
+
+    def _add_shared(self, out, h, step):
+        if self.shared is None:
+            return out
+        from ..csrc import ops
+        return ops.scaled_sum(out, 1.0, self.shared(h, step), 1.0, out)

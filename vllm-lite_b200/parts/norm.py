@@ -15,14 +15,23 @@ class RmsNorm:
 
     @staticmethod
     def declare(spec: NormSpec) -> dict:
-        return {spec.tensor: TensorDecl(() if spec.scalar else (spec.size,), init="norm")}
+        if not spec.has_weight:
+            return {}
+        # a weight stored around zero (offset + w) starts around zero in the random-weights mode as well
+        return {spec.tensor: TensorDecl(() if spec.scalar else (spec.size,), init="linear" if spec.offset else "norm")}
 
     def __init__(self, spec: NormSpec, weights: dict, ctx):
         self.spec = spec
         self.dtype = ctx.dtype
         # A vector of `size` numbers: kept as float32 on the device (exact from bfloat16).  A norm with one number
-        # for all coordinates holds that number `size` times, so every kernel sees a vector.
-        w = weights[spec.tensor].to(device=ctx.device, dtype=torch.float32)
+        # for all coordinates holds that number `size` times, so every kernel sees a vector; a norm without a tensor
+        # holds ones; a weight stored around zero is kept as offset + w (one float32 rounding, done once).
+        if not spec.has_weight:
+            w = torch.ones(spec.size, dtype=torch.float32, device=ctx.device)
+        else:
+            w = weights[spec.tensor].to(device=ctx.device, dtype=torch.float32)
+            if spec.offset:
+                w = w + float(spec.offset)
         self.weight = (w.reshape(1).expand(spec.size) if spec.scalar else w).contiguous()
 
     adds_bias = True           # add_normed takes the bias that the sub-layer's last product left out

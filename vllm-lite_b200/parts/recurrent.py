@@ -1,5 +1,6 @@
 """Mixers that keep a state of fixed size per request instead of a growing cache: a selective state space, a
-matrix memory with exponential gates, and a delta rule with a decay per key channel.
+matrix memory with exponential gates, a delta rule with a decay per key channel, and a memory with a decay per key
+channel behind token shifts (time mixing).
 
 Each is: one stacked projection of the input -> (a short causal convolution) -> a scan over the step's tokens from
 the state in the request's slot (csrc/recurrent.cu; a decoded token is a portion of one token) -> a gated RMS norm ->
@@ -14,7 +15,7 @@ import torch
 from ..cache.spec import FixedState
 from .linear import Linear
 from .registry import MIXERS
-from .spec import DeltaRuleSpec, MatrixMemorySpec, StateSpaceSpec, TensorDecl
+from .spec import DeltaRuleSpec, MatrixMemorySpec, StateSpaceSpec, TensorDecl, TimeMixSpec
 
 
 def _f32(t, ctx):
@@ -178,3 +179,68 @@ class DeltaRule:
         gated = ws.get(tag + "dr.gated", (T, H * P), self.dtype)
         ops.gate_norm(o, up, H * D, "sigmoid", False, self.norm, s.eps, gated, P)
         return self.o_proj(gated, step, "dr.out")
+
+
+@MIXERS.register("time_mix")
+class TimeMix:
+    """A memory per head with a decay per key channel, read through five token shifts of the input (`TimeMixSpec`).
+
+    token shifts (one kernel, five mixes) -> W_r, W_k, W_v, W_g, W_w1 each on its own mix -> tanh -> W_w2 -> the scan
+    (`ops.decay_scan`: decays exp(-exp(z + w0)) and the bonus u for the current token inside it) -> RMS norm per head,
+    weight, silu gate (`ops.gate_norm`) -> W_o.  The state of a request is one row of float32: the input row of its last
+    token, then the heads' memories in the scan's own layout.  r, k, v and the raw decay leave their products in float32
+    (the products add in float32 anyway), so nothing that enters the recurrence is rounded to the model's dtype."""
+    graph_safe = True
+    MIXES = "rkvgw"
+
+    @staticmethod
+    def declare(s: TimeMixSpec) -> dict:
+        mu, r, k, v, g, w1, w2, w0, u, norm, o = s.names
+        HD, W = s.num_heads * s.dim, s.hidden_size
+        d = {mu + m: TensorDecl((W,), init="unit") for m in TimeMix.MIXES}
+        d.update({r: TensorDecl((HD, W)), k: TensorDecl((HD, W)), v: TensorDecl((HD, W)), g: TensorDecl((HD, W)),
+                  w1: TensorDecl((s.decay_rank, W)), w2: TensorDecl((HD, s.decay_rank)), w0: TensorDecl((HD,), init="unit"),
+                  u: TensorDecl((s.num_heads, s.dim), init="unit"), norm: TensorDecl((HD,), init="norm"),
+                  o: TensorDecl((W, HD))})
+        return d
+
+    @staticmethod
+    def cache_need(s: TimeMixSpec):
+        from ..csrc import ops
+        return FixedState((s.hidden_size + ops.scan_state_floats(s.num_heads, s.dim, s.dim),))
+
+    def __init__(self, s: TimeMixSpec, weights: dict, ctx):
+        from ..csrc import ops
+        if s.num_heads <= 0 or s.dim <= 0 or s.decay_rank <= 0:
+            raise ValueError(f"time mix: {s.num_heads} heads of {s.dim}, decay rank {s.decay_rank}")
+        ops.scan_lanes(s.dim)
+        self.spec, self.dtype = s, ctx.dtype
+        mu, r, k, v, g, w1, w2, w0, u, norm, o = s.names
+        self.mu = _f32(torch.stack([weights[mu + m] for m in self.MIXES]), ctx)          # [5, W]
+        self.r, self.k, self.v, self.g = (Linear(weights[n]) for n in (r, k, v, g))
+        self.w1, self.w2 = Linear(weights[w1]), Linear(weights[w2])
+        self.o_proj = Linear(weights[o])
+        self.w0, self.u, self.norm = _f32(weights[w0], ctx), _f32(weights[u].reshape(-1), ctx), _f32(weights[norm], ctx)
+
+    def __call__(self, h, step, cache):
+        from ..csrc import ops
+        s, ws, tag = self.spec, step.workspace, step.tag
+        H, D, W = s.num_heads, s.dim, s.hidden_size
+        T = h.shape[0]
+        mixes = ws.get(tag + "tm.mix", (len(self.MIXES), T, W), self.dtype)
+        ops.token_shift_multi(h, self.mu, cache.state, 0, step.cu_seqlens, step.state_slots, step.req_index, step.positions,
+                              mixes)
+        f32 = torch.float32
+        r = self.r(mixes[0], step, "tm.r", out_dtype=f32)
+        k = self.k(mixes[1], step, "tm.k", out_dtype=f32)
+        v = self.v(mixes[2], step, "tm.v", out_dtype=f32)
+        g = self.g(mixes[3], step, "tm.g")
+        low = self.w1(mixes[4], step, "tm.w1")
+        low = ops.unary_act(low, ws.get(tag + "tm.w1t", tuple(low.shape), low.dtype), "tanh")
+        z = self.w2(low, step, "tm.w2", out_dtype=f32)
+        o = ws.get(tag + "tm.o", (T, H * D), f32)
+        ops.decay_scan((r, 0), (k, 0), (v, 0), (z, 0), self.w0, self.u, cache.state, W, step.cu_seqlens, step.state_slots, o,
+                       H, D, D)
+        gated = ws.get(tag + "tm.gated", (T, H * D), self.dtype)
+        ops.gate_norm(o, g, 0, "silu", False, self.norm, s.eps, gated, D)
+        return self.o_proj(gated, step, "tm.out")

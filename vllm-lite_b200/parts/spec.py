@@ -23,7 +23,7 @@ class TensorDecl:
 
     `init` names the distribution of the random-weights mode: "linear"
     (N(0, std)), "norm" (1 + N(0, norm_std)), "identity" (a square matrix: I + N(0, norm_std)), "conv" / "unit" (N(0, 0.5): taps of a short convolution, biases and
-    logarithms of gates and decays).  `store` is the dtype the tensor
+    logarithms of gates and decays), "rate" (0.05 + |N(0, 0.5)|: a positive factor).  `store` is the dtype the tensor
     has in a written folder and the least precision it is kept in:
     "model" (the model dtype, bfloat16 on disk) or "float32".
     """
@@ -38,7 +38,9 @@ class NormSpec:
     no bias) or "dyn_tanh" (tanh(alpha x) * w + b, alpha a learned scalar: no mean, no variance, eps unused).
     `tensor`: the weight's name relative to the norm's prefix ("" when the prefix is the whole name); a norm with
     a bias vector or a scalar stores them as `tensor + bias_suffix` / `tensor + alpha_suffix`.
-    `scalar`: the weight is ONE stored number for all `size` coordinates (an "rms_norm" only)."""
+    `scalar`: the weight is ONE stored number for all `size` coordinates (an "rms_norm" only).
+    `offset`: the stored weight lies around zero and the factor is offset + w (an "rms_norm" only; 0: the weight as stored).
+    `has_weight` False: no tensor at all, the factor is 1 (an "rms_norm" only)."""
     size: int
     eps: float
     kind: str = "rms_norm"
@@ -46,6 +48,8 @@ class NormSpec:
     bias_suffix: str = ".b"
     alpha_suffix: str = ".alpha"
     scalar: bool = False
+    offset: float = 0.0
+    has_weight: bool = True
 
 
 @dataclass(frozen=True)
@@ -72,6 +76,17 @@ class AttentionSpec:
     query's own position included).  `qk_norm`: norm over head_dim applied to
     every q and k head before the position encoding.  `scale` defaults to
     head_dim ** -0.5.
+
+    Options on the scores and around them, each on its own (all off by default):
+    `q_temp` (coef, every): the normed query at position p is multiplied by 1 + coef ln(floor((p + 1) / every) + 1);
+    `v_norm`: every value head is divided by its root mean square over its own size (an RMS norm without a weight,
+    with this eps) before it is cached;
+    `softcap` c: score <- c tanh(score / c) after the scale;
+    `distance_bias` (name a, name b): tensors [num_heads] each; a[h] ln(1 + b[h] (i - j)) is taken off the capped score
+    of the key j that query i reads;
+    `unit_sink`: the softmax denominator holds one more term exp(0) = 1, with no key and no value;
+    `gate` (a tensor name): the concatenated heads are multiplied element by element by sigmoid(W_g h),
+    W_g [num_heads * value size, hidden], before the output projection.
     """
     hidden_size: int
     num_heads: int
@@ -90,6 +105,12 @@ class AttentionSpec:
     names: Tuple[str, str, str, str] = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight")
     bias_names: Tuple[str, str, str, str] = ("q_proj.bias", "k_proj.bias", "v_proj.bias", "o_proj.bias")
     norm_prefixes: Tuple[str, str] = ("q_norm.", "k_norm.")
+    q_temp: Optional[Tuple[float, int]] = None
+    v_norm: Optional[float] = None
+    softcap: Optional[float] = None
+    distance_bias: Optional[Tuple[str, str]] = None
+    unit_sink: bool = False
+    gate: Optional[str] = None
 
 
 @dataclass(frozen=True)
@@ -132,8 +153,13 @@ class LatentAttentionSpec:
     c_q = rmsnorm(W_dq h), q = W_uq c_q (heads x dim); c = rmsnorm(W_dkv h) (kv_rank, the cached row);
     k_h = W_uk[h] c (dim), v_h = W_uv[h] c (vdim); scores scale * q.k over the last `window` positions
     (None: all earlier ones); `sink`: a learned number per head joins every softmax denominator;
-    out = W_o concat_h(sum p v).  No position encoding.  `names`: the tensors' names relative to the mixer's
-    prefix, in the order (dq, dq norm, uq, dkv, dkv norm, uk, uv, o, sink)."""
+    out = W_o concat_h(sum p v).  `names`: the tensors' names relative to the mixer's
+    prefix, in the order (dq, dq norm, uq, dkv, dkv norm, uk, uv, o, sink).
+    No position encoding unless `rot_dim` > 0: every query head then has rot_dim more features behind its `dim`
+    (W_uq has heads * (dim + rot_dim) rows), W_dkv has rot_dim more rows behind the latent's, which are NOT normed and
+    are ONE more key part shared by all heads; `position` turns the first `position.dim` features of both parts, and the
+    score is scale * (q . k + q_rot . k_rot).  The cached row is then [c | rotated key part].
+    `gate` (a tensor name): the concatenated heads times sigmoid(W_g h), W_g [heads * vdim, hidden], before W_o."""
     hidden_size: int
     num_heads: int
     dim: int
@@ -146,13 +172,18 @@ class LatentAttentionSpec:
     sink: bool = False
     names: Tuple[str, ...] = ("dq", "dq.norm", "uq", "dkv", "dkv.norm", "uk", "uv", "o", "sink")
     kind: str = "latent_attention"
+    rot_dim: int = 0
+    position: Optional[RotarySpec] = None
+    gate: Optional[str] = None
 
 
 @dataclass(frozen=True)
 class GatedMlpSpec:
     """down(act(gate(h)) * up(h)) with a choice of activation ("silu", "relu", or "capped_swish": g' = min(g, limit),
     u' = clamp(u, -limit, limit), g' sigmoid(alpha g') (u' + up_shift)) and optional bias vectors on all
-    three projections.  `names`: (gate, up, down) relative to the part's prefix; a bias is `<name><bias_suffix>`."""
+    three projections.  `names`: (gate, up, down) relative to the part's prefix; a bias is `<name><bias_suffix>`.
+    `gated` False: down(f(up(h))) with f a function of one argument ("relu2": the square of max(v, 0)); there is no gate
+    matrix and no bias."""
     hidden_size: int
     intermediate_size: int
     activation: str = "silu"
@@ -163,6 +194,7 @@ class GatedMlpSpec:
     names: Tuple[str, str, str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
     bias_suffix: str = ".b"
     kind: str = "gated_mlp"
+    gated: bool = True
 
 
 @dataclass(frozen=True)
@@ -177,6 +209,11 @@ class RoutedExpertsSpec:
     `gated` False: an expert is down(f(up y)) with f a function of one argument ("relu2": the square of max(v, 0)),
     and has no gate matrix.  `router_bias`: a vector `router + router_bias` added to the logits.  Score "softmax"
     with `renormalize` is the softmax over the chosen logits alone.
+    `choice_bias` (a tensor name, [num_experts]): experts, and groups, are chosen by score + choice_bias; the weights are
+    the scores without it.  `group_top`: a group's score is the sum of that many of its largest choice values (1: its
+    largest).  `renorm_eps` is added to the sum that `renormalize` divides by.
+    `shared`: the description of one more feed-forward (any registered kind) that runs for every token and is added; its
+    tensors lie under `shared_prefix`.
     Tensors: `router`, and per expert i `expert_prefix.format(i)` + gate / up / down of `names`."""
     hidden_size: int
     intermediate_size: int
@@ -199,6 +236,11 @@ class RoutedExpertsSpec:
     kind: str = "routed_experts"
     gated: bool = True
     router_bias: Optional[str] = None
+    choice_bias: Optional[str] = None
+    group_top: int = 1
+    renorm_eps: float = 0.0
+    shared: Optional[object] = None
+    shared_prefix: str = "shared."
 
 
 @dataclass(frozen=True)
@@ -314,6 +356,25 @@ class TokenShiftSpec:
 
 
 @dataclass(frozen=True)
+class TimeMixSpec:
+    """A memory per head with a decay per key channel, read through token shifts (time mixing in the manner of RWKV).
+
+    With h' the row of the token before (zeros before a sequence's first token; the last row is part of the state), each of
+    r, k, v, g, w reads its own mix h + (h' - h) * mu_s.  r, k, v = W_r, W_k, W_v of their mixes (heads x dim each),
+    gate = silu(W_g mix_g), decay = exp(-exp(W_w2 tanh(W_w1 mix_w) + w0)) per head and key channel (`decay_rank`: rows of
+    W_w1).  Per head, S [dim x dim] from zero: o_t = (S + diag(u) k_t v_t^T)^T r_t, then S <- diag(decay_t) S + k_t v_t^T.
+    out = W_o (rms_head(o) * norm * gate), the RMS norm over every head's dim values with `eps`, no weight but `norm`
+    [heads * dim].  `names`: (mu prefix, r, k, v, g, w1, w2, w0, u, norm, o); the five mu are `<mu prefix><s>`."""
+    hidden_size: int
+    num_heads: int
+    dim: int
+    decay_rank: int
+    eps: float
+    names: Tuple[str, ...] = ("mu.", "r", "k", "v", "g", "w1", "w2", "w0", "u", "norm", "o")
+    kind: str = "time_mix"
+
+
+@dataclass(frozen=True)
 class ParallelMixerSpec:
     """Two mixers side by side on the same input: left_scale * left(h) + right_scale * right(h).  Each keeps its own
     cache or state; their tensors lie under `prefixes`."""
@@ -348,7 +409,9 @@ class BlockSpec:
     kind "hyper_connection": `streams` copies x_1..x_S of the stream (all equal to the single stream when the first
     such block meets it); sub-layer q reads u = sum_s in_q[s] x_s through its norm and writes
     x_t <- sum_s mix_q[s, t] x_s + out_q[t] y; the single stream is the sum of the copies.  `hyper`: the two
-    sub-layers' `HyperConnectionSpec`; `hyper_prefixes`: where their tensors lie.  `ffn` may be None."""
+    sub-layers' `HyperConnectionSpec`; `hyper_prefixes`: where their tensors lie.  `ffn` may be None.
+    kind "sandwich": x += post1(mixer(norm1(x))); x += post2(ffn(norm2(x))): a norm before and a norm after every
+    sub-layer (`post_norms`, their tensors under `post_names`); `ffn` may be None."""
     mixer: object
     ffn: object
     norm1: NormSpec
@@ -360,6 +423,8 @@ class BlockSpec:
     residual_mult: float = 1.0      # post_norm: the factor on every normed sub-layer output
     # tensor-name prefixes of the four parts inside a layer (norm1, mixer, norm2, feed-forward)
     names: Tuple[str, str, str, str] = ("input_layernorm.", "self_attn.", "post_attention_layernorm.", "mlp.")
+    post_norms: Optional[Tuple[NormSpec, NormSpec]] = None     # sandwich: the norms on the two sub-layers' outputs
+    post_names: Tuple[str, str] = ("post_mixer_norm.", "post_mlp_norm.")
 
 
 @dataclass(frozen=True)

@@ -110,6 +110,8 @@ def random_tensors(declared: dict, seed: int, std: float = 0.02, norm_std: float
             t = t.mul_(std)
         elif decl.init in ("conv", "unit"):
             t = t.mul_(0.5)
+        elif decl.init == "rate":
+            t = t.abs_().mul_(0.5).add_(0.05)
         elif decl.init == "identity":
             t = t.mul_(norm_std).add_(torch.eye(decl.shape[0], device=t.device))
         else:
