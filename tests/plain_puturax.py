@@ -225,3 +225,25 @@ def forward(config, weights, tokens):
         streams.append(x)
     logits = lin(w["embed"], offset_norm(x, w["final.norm"], eps))
     return logits, torch.stack(streams)
+
+
+def read_model_dir(folder):
+    """(config.json as a dict, {name: tensor}) of a model folder; a reader of its own: 8 bytes of length, a JSON
+    header name -> (dtype, shape, data_offsets), then the data."""
+    import json
+    import struct
+    from pathlib import Path
+    folder = Path(folder)
+    config = json.loads((folder / "config.json").read_text())
+    raw = (folder / "model.safetensors").read_bytes()
+    n = struct.unpack("<Q", raw[:8])[0]
+    header = json.loads(raw[8:8 + n])
+    kinds = {"BF16": torch.bfloat16, "F32": torch.float32, "F16": torch.float16}
+    weights = {}
+    for name, info in header.items():
+        if name == "__metadata__":
+            continue
+        lo, hi = info["data_offsets"]
+        t = torch.frombuffer(bytearray(raw[8 + n + lo:8 + n + hi]), dtype=kinds[info["dtype"]])
+        weights[name] = t.reshape(info["shape"]).clone()
+    return config, weights

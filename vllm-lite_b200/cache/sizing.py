@@ -47,12 +47,15 @@ def _mixer_width(mixer) -> int:
         return _mixer_width(mixer.left) + _mixer_width(mixer.right) + 2 * getattr(mixer.left, "hidden_size", 0)
     if hasattr(mixer, "num_kv_heads") and hasattr(mixer, "head_dim"):
         hd = max(mixer.head_dim, getattr(mixer, "v_head_dim", None) or 0)
-        return (2 * mixer.num_heads + 2 * mixer.num_kv_heads) * (-(-hd // 16) * 16)
+        gate = mixer.num_heads if getattr(mixer, "gate", None) else 0  # an output gate as wide as the heads
+        return (2 * mixer.num_heads + 2 * mixer.num_kv_heads + gate) * (-(-hd // 16) * 16)
     if hasattr(mixer, "kv_rank"):
-        # latent attention: both latents, the queries, their absorbed form and the context (heads x cached row, the
-        # row rounded up to 16), the expanded values
-        row = -(-mixer.kv_rank // 16) * 16
-        return mixer.q_rank + mixer.kv_rank + mixer.num_heads * (mixer.dim + 2 * row + mixer.vdim)
+        # latent attention: both latents (and the rotated key part), the queries, their absorbed form and the context
+        # (heads x cached row, the row rounded up to 16), the expanded values, the output gate
+        rot = getattr(mixer, "rot_dim", 0)
+        row = -(-(mixer.kv_rank + rot) // 16) * 16
+        gate = mixer.num_heads * mixer.vdim if getattr(mixer, "gate", None) else 0
+        return mixer.q_rank + mixer.kv_rank + rot + gate + mixer.num_heads * (mixer.dim + rot + 2 * row + mixer.vdim)
     if hasattr(mixer, "state") and hasattr(mixer, "norm_groups"):       # state space: projection, convolved copy, scan, gated
         inner = mixer.num_heads * mixer.vdim
         conv = inner + 2 * mixer.groups * mixer.state
@@ -60,6 +63,10 @@ def _mixer_width(mixer) -> int:
     if hasattr(mixer, "gate_cap"):                                      # matrix memory
         hp, hd = mixer.num_heads * mixer.vdim, mixer.num_heads * mixer.dim
         return (2 * hd + 2 * hp + 2 * mixer.num_heads) + 2 * hp + hp
+    if hasattr(mixer, "decay_rank") and not hasattr(mixer, "gate_rank"):
+        # time mixing: five mixes of the input, r, k, v and the raw decay in float32, the gate, the scan's result, the gated rows
+        hd = mixer.num_heads * mixer.dim
+        return 5 * mixer.hidden_size + 8 * hd + hd + 2 * mixer.decay_rank + 2 * hd + hd
     if hasattr(mixer, "decay_rank"):                                    # delta rule
         hp, hd = mixer.num_heads * mixer.vdim, mixer.num_heads * mixer.dim
         conv = 2 * mixer.num_kv_heads * mixer.dim + hp

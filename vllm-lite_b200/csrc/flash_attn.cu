@@ -79,7 +79,26 @@ struct AttnOptions {
     int block;                                           // positions per block of the mask (0: none)
     const float* head_bias;                              // (SIG) a number per query head added to every score, or null
     const bf16* gate; int gate_stride;                   // a gate logit per (token of the step, head), or null
+    float cap_l2;                                        // a bound on the scores, times log2 e (0: none): s <- cap tanh(s / cap)
+    const float* dist_a; const float* dist_b;            // per query head (or null): a ln(1 + b (i - j)) is taken off the score
 };
+// A score y (already scaled, in units of log2) bounded by cap_l2 and less the bias of a key `dist` positions back, still in
+// units of log2: cap tanh(y / cap), tanh(z) = 1 - 2 / (1 + e^(2z)); a ln(1 + b d) log2 e = a log2(1 + b d).
+__device__ __forceinline__ float shape_score(float y, float cap_l2, float two_over_cap, float da, float db, int dist) {
+    if (cap_l2 > 0.f) {
+        float r;
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + exp2_mufu(y * two_over_cap)));
+        y = cap_l2 - 2.f * cap_l2 * r;
+    }
+    if (da != 0.f) {
+        float l;
+        asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(l) : "f"(fmaf(db, (float)dist, 1.f)));
+        y -= da * l;
+    }
+    return y;
+}
+// 2 log2(e) / cap_l2: what a score in units of log2 is multiplied by to give the exponent of 2 that is e^(2 s / cap)
+__device__ __forceinline__ float two_over_cap(float cap_l2) { return cap_l2 > 0.f ? 2.f * 1.4426950408889634f / cap_l2 : 0.f; }
 __device__ __forceinline__ float gate_factor(const AttnOptions& op, int tok, int h) {
     return op.gate ? 1.f / (1.f + __expf(-__bfloat162float(op.gate[(size_t)tok * op.gate_stride + h]))) : 1.f;
 }
@@ -179,6 +198,9 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     const bool row_a = row0 + g < count, row_b = row0 + g + 8 < count;
     const int blk_a = op.block > 0 ? pos_a / op.block * op.block : 0, blk_b = op.block > 0 ? pos_b / op.block * op.block : 0;
     const float bias_log2 = (SIG && op.head_bias) ? op.head_bias[h] * 1.4426950408889634f : 0.f;
+    const bool shaped = op.cap_l2 > 0.f || op.dist_a != nullptr;
+    const float sl2 = shaped ? 1.f : scale_log2;                 // shaped scores are in units of log2 already
+    const float toc = two_over_cap(op.cap_l2), da = op.dist_a ? op.dist_a[h] : 0.f, db = op.dist_a ? op.dist_b[h] : 0.f;
 
     for (int kt = kt_lo; kt <= kt_hi; ++kt) {
         const int buf = (kt - kt_lo) & 1;
@@ -216,6 +238,15 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
         // mask and online softmax.  The running maximum is kept in units of log2 (score * scale * log2 e);
         // the scale is applied inside the exponent: p = 2^(s * scale_log2 - base).
         const int j_base = kt * BN + 2 * t;
+        if (shaped) {                                            // (uniform) bounded scores, less the bias of the distance
+#pragma unroll
+            for (int n = 0; n < BN / 8; ++n) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    s[n][e] = shape_score(s[n][e] * scale_log2, op.cap_l2, toc, da, db,
+                                          ((e < 2) ? pos_a : pos_b) - (j_base + n * 8 + (e & 1)));
+            }
+        }
         const bool need_mask = (kt * BN + BN - 1 > pos0 + row0) || (window > 0) || !row_a || !row_b || kt * BN < blk_hi;
         float mx[2] = {-INFINITY, -INFINITY};
         if (need_mask) {
@@ -235,8 +266,8 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
             unsigned pf[BN / 16][4];
 #pragma unroll
             for (int n = 0; n < BN / 8; ++n) {
-                const float p0 = sigmoid_log2(fmaf(s[n][0], scale_log2, bias_log2)), p1 = sigmoid_log2(fmaf(s[n][1], scale_log2, bias_log2));
-                const float p2 = sigmoid_log2(fmaf(s[n][2], scale_log2, bias_log2)), p3 = sigmoid_log2(fmaf(s[n][3], scale_log2, bias_log2));
+                const float p0 = sigmoid_log2(fmaf(s[n][0], sl2, bias_log2)), p1 = sigmoid_log2(fmaf(s[n][1], sl2, bias_log2));
+                const float p2 = sigmoid_log2(fmaf(s[n][2], sl2, bias_log2)), p3 = sigmoid_log2(fmaf(s[n][3], sl2, bias_log2));
                 pf[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);
                 pf[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
             }
@@ -261,7 +292,7 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
         for (int r = 0; r < 2; ++r) {
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-            const float mn = fmaxf(m_run[r], mx[r] * scale_log2);       // scale_log2 > 0 keeps the order
+            const float mn = fmaxf(m_run[r], mx[r] * sl2);       // a factor > 0 keeps the order
             base[r] = (mn == -INFINITY) ? 0.f : mn;              // a row with no key yet: 2^(-inf - 0) = 0
             corr[r] = exp2_mufu(m_run[r] - base[r]);
             m_run[r] = mn;
@@ -271,8 +302,8 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
         unsigned pf[BN / 16][4];
 #pragma unroll
         for (int n = 0; n < BN / 8; ++n) {
-            const float p0 = exp2_mufu(fmaf(s[n][0], scale_log2, -base[0])), p1 = exp2_mufu(fmaf(s[n][1], scale_log2, -base[0]));
-            const float p2 = exp2_mufu(fmaf(s[n][2], scale_log2, -base[1])), p3 = exp2_mufu(fmaf(s[n][3], scale_log2, -base[1]));
+            const float p0 = exp2_mufu(fmaf(s[n][0], sl2, -base[0])), p1 = exp2_mufu(fmaf(s[n][1], sl2, -base[0]));
+            const float p2 = exp2_mufu(fmaf(s[n][2], sl2, -base[1])), p3 = exp2_mufu(fmaf(s[n][3], sl2, -base[1]));
             ls[0] += p0 + p1;
             ls[1] += p2 + p3;
             pf[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);
@@ -332,8 +363,10 @@ extern "C" int vl_flash_prefill(const void* q, int q_stride, void* out, const vo
                                 const int* block_table, int max_blocks, const int* tiles, int num_tiles, int tile_rows,
                                 int nq, int nkv, int hd, int page_size, int num_pages, float scale, int window,
                                 unsigned* err, const float* sinks, int weighting, int block, const float* head_bias,
-                                const void* gate, int gate_stride, void* stream) {
+                                const void* gate, int gate_stride, float softcap, const float* dist_a, const float* dist_b,
+                                void* stream) {
     if (num_tiles <= 0) return VL_OK;
+    if (softcap < 0.f || (dist_a == nullptr) != (dist_b == nullptr)) return VL_ERR_ARGUMENT;
     if (hd != HD) return VL_ERR_UNSUPPORTED;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || q_stride % 8) return VL_ERR_ARGUMENT;
     if (tile_rows <= 0 || tile_rows > 65536) return VL_ERR_ARGUMENT;
@@ -345,7 +378,7 @@ extern "C" int vl_flash_prefill(const void* q, int q_stride, void* out, const vo
     auto kernel = weighting == 1 ? flash_prefill_kernel<true> : flash_prefill_kernel<false>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    const AttnOptions op = {weighting, block, head_bias, (const bf16*)gate, gate_stride};
+    const AttnOptions op = {weighting, block, head_bias, (const bf16*)gate, gate_stride, softcap * 1.4426950408889634f, dist_a, dist_b};
     kernel<<<dim3(nq, num_tiles * parts), NTHREADS, smem, (cudaStream_t)stream>>>(
         (const bf16*)q, q_stride, (bf16*)out, (const bf16*)kcache, (const bf16*)vcache, block_table, max_blocks,
         (const int4*)tiles, parts, nq, nkv, page_size, num_pages, scale * 1.4426950408889634f, window, err, sinks, op);
@@ -623,6 +656,13 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
         }
 #pragma unroll
         for (int d = 0; d < MT; ++d) { oT[d][0] = oT[d][1] = oT[d][2] = oT[d][3] = 0.f; }
+        const bool shaped = fz.op.cap_l2 > 0.f || fz.op.dist_a != nullptr;
+        const float toc = two_over_cap(fz.op.cap_l2);
+        float da[2] = {0.f, 0.f}, db[2] = {0.f, 0.f};            // the distance bias of heads 2t and 2t + 1
+        if (fz.op.dist_a) {
+            da[0] = fz.op.dist_a[h0 + min(2 * t, nvalid - 1)]; db[0] = fz.op.dist_b[h0 + min(2 * t, nvalid - 1)];
+            da[1] = fz.op.dist_a[h0 + min(2 * t + 1, nvalid - 1)]; db[1] = fz.op.dist_b[h0 + min(2 * t + 1, nvalid - 1)];
+        }
         unsigned qb[KSTEPS][2];                                  // Q^T as the 16 x 8 operand: features 2t.., 2t + 8.. of head g
         cp_async_wait<DEC_NST - 1>();                            // this thread's share of the query rows has landed ...
         __syncthreads();                                         // ... and so has everybody's
@@ -649,8 +689,15 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
             }
             const int j0 = st * BN + warp * 16 + g;              // this lane's keys: j0 and j0 + 8
             const bool in0 = j0 >= c0 && j0 < c1, in1 = j0 + 8 >= c0 && j0 + 8 < c1;
-            sT[0] = in0 ? sT[0] * scale_log2 : -INFINITY; sT[1] = in0 ? sT[1] * scale_log2 : -INFINITY;
-            sT[2] = in1 ? sT[2] * scale_log2 : -INFINITY; sT[3] = in1 ? sT[3] * scale_log2 : -INFINITY;
+            if (shaped) {                                        // (uniform) bounded scores, less the bias of the distance
+                sT[0] = in0 ? shape_score(sT[0] * scale_log2, fz.op.cap_l2, toc, da[0], db[0], pos - j0) : -INFINITY;
+                sT[1] = in0 ? shape_score(sT[1] * scale_log2, fz.op.cap_l2, toc, da[1], db[1], pos - j0) : -INFINITY;
+                sT[2] = in1 ? shape_score(sT[2] * scale_log2, fz.op.cap_l2, toc, da[0], db[0], pos - j0 - 8) : -INFINITY;
+                sT[3] = in1 ? shape_score(sT[3] * scale_log2, fz.op.cap_l2, toc, da[1], db[1], pos - j0 - 8) : -INFINITY;
+            } else {
+                sT[0] = in0 ? sT[0] * scale_log2 : -INFINITY; sT[1] = in0 ? sT[1] * scale_log2 : -INFINITY;
+                sT[2] = in1 ? sT[2] * scale_log2 : -INFINITY; sT[3] = in1 ? sT[3] * scale_log2 : -INFINITY;
+            }
             float corr[2] = {1.f, 1.f}, p0, p1, p2, p3;
             if constexpr (SIG) {                                 // every key by itself; the sums stay relative to 0
                 p0 = sigmoid_log2(sT[0] + hb[0]); p1 = sigmoid_log2(sT[1] + hb[1]);
@@ -713,6 +760,13 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
         }
 #pragma unroll
         for (int d = 0; d < DTILES; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+        const bool shaped = fz.op.cap_l2 > 0.f || fz.op.dist_a != nullptr;
+        const float toc = two_over_cap(fz.op.cap_l2);
+        float da[2] = {0.f, 0.f}, db[2] = {0.f, 0.f};                // the distance bias of heads g and g + 8
+        if (fz.op.dist_a) {
+            da[0] = fz.op.dist_a[h0 + min(g, nvalid - 1)]; db[0] = fz.op.dist_b[h0 + min(g, nvalid - 1)];
+            da[1] = fz.op.dist_a[h0 + min(g + 8, nvalid - 1)]; db[1] = fz.op.dist_b[h0 + min(g + 8, nvalid - 1)];
+        }
         unsigned qf[KSTEPS][4];
         cp_async_wait<DEC_NST - 1>();                                // this thread's share of the query rows has landed ...
         __syncthreads();                                             // ... and so has everybody's
@@ -744,7 +798,10 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int j = st * BN + kr0 + n * 8 + 2 * t + (e & 1);
-                    const float v = (j >= c0 && j < c1) ? s[n][e] * scale_log2 : -INFINITY;
+                    float v = -INFINITY;
+                    if (j >= c0 && j < c1)
+                        v = shaped ? shape_score(s[n][e] * scale_log2, fz.op.cap_l2, toc, da[e >> 1], db[e >> 1], pos - j)
+                                   : s[n][e] * scale_log2;
                     s[n][e] = v;
                     mx[e >> 1] = fmaxf(mx[e >> 1], v);
                 }
@@ -1029,10 +1086,12 @@ extern "C" int vl_flash_decode(const void* q, int q_stride, const void* kcache, 
                                int T, int nq, int nkv, int hd, int page_size, int num_pages, float scale, int window,
                                int chunk, int S, float* part_acc, float* part_ml, unsigned* err,
                                const int* token_index, void* out, int* arrivals, const float* sinks, int weighting,
-                               int block, const float* head_bias, const void* gate, int gate_stride, void* stream) {
+                               int block, const float* head_bias, const void* gate, int gate_stride, float softcap,
+                               const float* dist_a, const float* dist_b, void* stream) {
+    if (softcap < 0.f || (dist_a == nullptr) != (dist_b == nullptr)) return VL_ERR_ARGUMENT;
     DecodeFusion fz = {};
     fz.sinks = sinks;
-    fz.op = AttnOptions{weighting, block, head_bias, (const bf16*)gate, gate_stride};
+    fz.op = AttnOptions{weighting, block, head_bias, (const bf16*)gate, gate_stride, softcap * 1.4426950408889634f, dist_a, dist_b};
     return launch_flash_decode(q, q_stride, kcache, vcache, block_table, max_blocks, req_index, positions, T, nq, nkv, hd,
                                page_size, num_pages, scale, window, chunk, S, part_acc, part_ml, err, token_index, out,
                                arrivals, fz, stream);

@@ -71,14 +71,14 @@ _SIGNATURES = {
                                                  c_int, c_int, c_void_p, c_void_p, c_void_p],
     ("flash_attn", "vl_flash_prefill"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                          c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
-                                         c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
+                                         c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p],
     ("flash_tc5", "vl_flash_prefill_tc5"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                             c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
                                             c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
     ("flash_attn", "vl_flash_decode"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
                                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                        c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
+                                        c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p],
     ("flash_attn", "vl_flash_decode_fused"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                               c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
                                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -567,14 +567,17 @@ def _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, h
 
 
 def flash_prefill(qkv, out, k_cache, v_cache, block_table, tiles, num_heads, num_kv_heads, head_dim, scale, window, err,
-                  tile_rows=64, sinks=None, weighting="softmax", mask_chunk=None, head_bias=None, gate=None):
+                  tile_rows=64, sinks=None, weighting="softmax", mask_chunk=None, head_bias=None, gate=None, softcap=None,
+                  distance=None):
     """Tensor-core (mma.sync) attention for prompt portions.  `tiles` int32 [n, 4]: (row of the block
     table, index of the tile's first token in the step, tokens (<= tile_rows), position of the first
     token); the tiles of a step cover every token that the kernel is to serve once.
-    `weighting`, `mask_chunk` (the `chunk` there), `head_bias`, `gate`: see `_check_variant`."""
+    `weighting`, `mask_chunk` (the `chunk` there), `head_bias`, `gate`: see `_check_variant`; `softcap`, `distance`: see
+    `_check_score_shape`."""
     _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, head_dim)
     _check_sinks(sinks, num_heads)
     mode, mask_chunk, gate_stride = _check_variant(qkv, num_heads, weighting, mask_chunk, head_bias, gate, sinks)
+    cap, dist_a, dist_b = _check_score_shape(num_heads, softcap, distance)
     _need(out, torch.bfloat16, "out", 2); _need(tiles, torch.int32, "tiles", 2)
     if out.shape != (qkv.shape[0], num_heads * head_dim) or tiles.shape[1] != 4:
         raise KernelError("flash_prefill: shapes disagree")
@@ -582,7 +585,7 @@ def flash_prefill(qkv, out, k_cache, v_cache, block_table, tiles, num_heads, num
         _ptr(qkv), qkv.shape[1], _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
         _ptr(tiles), tiles.shape[0], int(tile_rows), num_heads, num_kv_heads, head_dim, k_cache.shape[2],
         k_cache.shape[0], float(scale), int(window or 0), _ptr(err), _ptr(sinks), mode, mask_chunk, _ptr(head_bias),
-        _ptr(gate), gate_stride, _stream()), "vl_flash_prefill")
+        _ptr(gate), gate_stride, cap, _ptr(dist_a), _ptr(dist_b), _stream()), "vl_flash_prefill")
     return out
 
 
@@ -651,7 +654,7 @@ def flash_decode_streams(dtype, num_tokens, num_kv_heads, head_dim, page_size, m
 def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, num_heads, num_kv_heads,
                  head_dim, scale, window, max_context, part_acc, part_ml, err, chunk=DECODE_CHUNK, token_index=None,
                  stream_kernel=None, arrivals=None, fold=None, sinks=None, weighting="softmax", mask_chunk=None,
-                 head_bias=None, gate=None):
+                 head_bias=None, gate=None, softcap=None, distance=None):
     """Tensor-core version of `decode_attention` (bfloat16): every block takes a chunk of a token's
     keys; the chunks are merged by the block that finishes last (`arrivals`: int32 counters,
     `flash_decode_arrivals` of them, zero before the first call and left zero) or, without
@@ -666,13 +669,19 @@ def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, 
     projection left them, every token is the last of its request, and the token's key and value are
     written to the cache by this launch (slots None: not written).  The same bits as the two kernels in turn.
     `weighting`, `mask_chunk` (the `chunk` there), `head_bias`, `gate`: see `_check_variant`.  The sigmoid and the gate
-    go with the block-per-chunk kernel that merges its chunks itself (`arrivals` given, few enough chunks)."""
+    go with the block-per-chunk kernel that merges its chunks itself (`arrivals` given, few enough chunks).
+    `softcap`, `distance` (see `_check_score_shape`) go with the block-per-chunk kernel, merged either way."""
     _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, head_dim)
     _check_sinks(sinks, num_heads)
     mode, mask_chunk, gate_stride = _check_variant(qkv, num_heads, weighting, mask_chunk, head_bias, gate, sinks)
+    cap, dist_a, dist_b = _check_score_shape(num_heads, softcap, distance)
     variant = bool(mode or mask_chunk or gate is not None)
-    if variant and fold is not None:
+    if (variant or cap or dist_a is not None) and fold is not None:
         raise KernelError("flash_decode: the folded head work goes with the plain softmax")
+    if cap or dist_a is not None:
+        if stream_kernel:
+            raise KernelError("flash_decode: capped or biased scores go with the block-per-chunk kernel")
+        stream_kernel = False
     if sinks is not None and fold is not None:
         raise KernelError("flash_decode: the folded head work and sinks do not go together")
     _need(out, torch.bfloat16, "out", 2)
@@ -710,7 +719,7 @@ def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, 
         if fold is None:
             _check(_fn("flash_attn", "vl_flash_decode", {"FA_HD": head_dim})(
                 *args, _ptr(out) if arrivals is not None else None, _ptr(arrivals), _ptr(sinks), mode, mask_chunk,
-                _ptr(head_bias), _ptr(gate), gate_stride, _stream()), "vl_flash_decode")
+                _ptr(head_bias), _ptr(gate), gate_stride, cap, _ptr(dist_a), _ptr(dist_b), _stream()), "vl_flash_decode")
         else:
             qw, kw, eps, inv_freq, rot, slots = fold
             for t, n in ((qw, "q_weight"), (kw, "k_weight"), (inv_freq, "inv_freq")):

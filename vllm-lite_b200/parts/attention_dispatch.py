@@ -36,7 +36,8 @@ def folds_head_work(dtype, step, spec, group, num_tokens) -> bool:
     return -(-int(group.max_context) // chunk) <= FOLD_MAX_CHUNKS
 
 
-def _decode(ops, args, step, spec, group, num_tokens, max_context, token_index=None, fold=None, sinks=None, variant=None):
+def _decode(ops, args, step, spec, group, num_tokens, max_context, token_index=None, fold=None, sinks=None, variant=None,
+            shape=None):
     chunk = ops.decode_chunk_for(num_tokens, spec.num_kv_heads, max_context, head_dim=spec.head_dim)
     own_merge = True
     if variant is not None:
@@ -58,7 +59,7 @@ def _decode(ops, args, step, spec, group, num_tokens, max_context, token_index=N
     arrivals = step.workspace.zeros(step.tag + "attn.arrivals", ops.flash_decode_arrivals(num_tokens, spec.num_heads, spec.num_kv_heads),
                                     torch.int32) if own_merge else None
     return ops.flash_decode(*args, max_context, part_acc, part_ml, step.err, chunk=chunk, token_index=token_index,
-                            arrivals=arrivals, fold=fold, sinks=sinks, **(variant or {}))
+                            arrivals=arrivals, fold=fold, sinks=sinks, **(variant or {}), **(shape or {}))
 
 
 def _variant_decode_ok(ops, spec, num_tokens, max_context, mask_chunk) -> bool:
@@ -137,7 +138,24 @@ def _run_variant(ops, q, out, cache, group, step, spec, scale, weighting, chunk,
 
 
 def _run_shaped(ops, q, out, cache, group, step, spec, scale, sinks, weighting, chunk, head_bias, gate, softcap, distance):
-    """Attention whose scores are capped or lose a bias that grows with the distance."""
+    """Attention whose scores are capped or lose a bias that grows with the distance: in bfloat16 the mma.sync kernel for
+    portions of prompts and the block-per-chunk kernel for single tokens (a mixed step launches both); in float32, for
+    other head sizes, or together with another weighting, a chunked mask or a gate per head, the one kernel whose sums
+    depend on positions alone."""
+    shape = dict(softcap=softcap, distance=distance)
+    plain = weighting == "softmax" and chunk is None and head_bias is None and gate is None
+    if plain and ops.flash_supported(q.dtype, spec.head_dim):
+        args = (q, out, cache.k, cache.v, group.block_table, step.req_index, step.positions,
+                spec.num_heads, spec.num_kv_heads, spec.head_dim, scale, spec.window)
+        if step.max_query_len == 1:
+            return _decode(ops, args, step, spec, group, q.shape[0], group.max_context, sinks=sinks, shape=shape)
+        if step.query_tiles is not None:
+            ops.flash_prefill(q, out, cache.k, cache.v, group.block_table, step.query_tiles, spec.num_heads, spec.num_kv_heads,
+                              spec.head_dim, scale, spec.window, step.err, tile_rows=QUERY_TILE, sinks=sinks, **shape)
+            if step.single_tokens is not None:
+                _decode(ops, args, step, spec, group, step.single_tokens.shape[0], step.single_context,
+                        token_index=step.single_tokens, sinks=sinks, shape=shape)
+            return out
     return ops.paged_attention(q, out, cache.k, cache.v, group.block_table, step.req_index, step.positions,
                                spec.num_heads, spec.num_kv_heads, spec.head_dim, scale, spec.window, step.err, sinks=sinks,
                                weighting=weighting, chunk=chunk, head_bias=head_bias, gate=gate, softcap=softcap,
