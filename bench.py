@@ -430,7 +430,8 @@ TIMED_OPS = ("paged_attention", "flash_prefill", "flash_prefill_tc5", "flash_dec
              "layernorm_rows", "add_rmsnorm", "latent_norm_write", "qk_norm_rope_write", "moe_route", "moe_align",
              "moe_gather", "moe_combine", "gated_act", "silu_mul", "scale_softcap", "embed", "cast", "add_bias",
              "hc_step", "dyt_rows", "short_conv", "ssd_scan", "mlstm_scan", "delta_scan", "gate_norm", "scaled_sum",
-             "token_shift", "rows_norm_rope_write", "conv_rows_norm_rope_write", "rmsnorm_add", "unary_act")
+             "token_shift", "rows_norm_rope_write", "conv_rows_norm_rope_write", "rmsnorm_add", "unary_act",
+             "head_norm_write", "rope_heads", "sigmoid_gate", "token_shift_multi", "decay_scan")
 
 
 def kikepel_config(size, layers):
@@ -458,7 +459,9 @@ def timed_step(runner, entries):
             e0.record()
             r = fn(*a, **k)
             e1.record()
-            records.append((name, e0, e1))
+            # an attention launch whose scores are capped or biased by the distance is listed apart
+            shaped = k.get("softcap") or k.get("distance") is not None
+            records.append((name + "+shape" if shaped else name, e0, e1))
             return r
         return inner
     for name in TIMED_OPS:
@@ -842,6 +845,148 @@ def sodonex_bench(args):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------------
+# --puturax: the Puturax decoder (norms before and after every sub-layer; latent attention with a rotated part; attention
+# with capped, distance-biased scores beside a time mixing; grouped experts with a shared one) beside the Qwen3 decoder
+# at equal width, depth, heads and active feed-forward width
+# ---------------------------------------------------------------------------------------------------
+# name: (width, heads, kv heads, head size, latent query rank, latent rank, rotated part, time-mixing heads, their size, decay rank,
+#        dense ff, expert ff, experts, top, groups, kept, shared ff, vocab)
+PUTURAX_SIZES = {"2k": (2048, 16, 4, 128, 768, 64, 64, 32, 64, 64, 8192, 1024, 32, 4, 4, 2, 1024, 65536),
+                 "4k": (4096, 32, 8, 128, 1536, 64, 64, 64, 64, 128, 12288, 1408, 64, 6, 8, 4, 1408, 65536),
+                 "4k-h64": (4096, 64, 8, 64, 1024, 96, 32, 32, 128, 64, 8192, 2048, 32, 4, 4, 3, 2048, 65536)}
+
+
+def puturax_config(size, layers):
+    W, H, KV, D, QR, KR, R, TH, TD, rank, ff, eff, E, top, groups, keep, sff, vocab = PUTURAX_SIZES[size]
+    lat = dict(heads=H, dim=D, rot_dim=R, vdim=D, q_rank=QR, kv_rank=KR, scale=(D + R) ** -0.5, rot=dict(dims=R, base=500000.0))
+    par = dict(left=dict(heads=H, kv_heads=KV, dim=D, vdim=D, scale=0.2, softcap=30.0,
+                         q_temp=dict(coef=0.1, every=1024)),
+               right=dict(heads=TH, dim=TD, decay_rank=rank), left_scale=0.7, right_scale=0.6)
+    moe = dict(kind="moe", expert=dict(ff=eff), router=dict(experts=E, top=top, groups=dict(count=groups, keep=keep)), shared=dict(ff=sff))
+    kinds = [("latent_attention", lat, dict(kind="dense", ff=ff)), ("parallel", par, moe), ("parallel", par, moe), ("parallel", par, moe)]
+    return dict(architecture="Puturax", vocab=vocab, width=W, norm=dict(eps=1e-6), embedding=dict(scale=W ** 0.5),
+                max_position_embeddings=16384,
+                layers=[dict(type=kinds[i % 4][0], mixer=kinds[i % 4][1], mlp=kinds[i % 4][2]) for i in range(layers)])
+
+
+def puturax_bench(args):
+    import torch
+    from vllm_lite_b200.engine import LLMEngine, StepEntry, random_model
+    size, layers = args.puturax, args.layers or 8
+    W, H, KV, D, QR, KR, R, TH, TD, rank, ff, eff, E, top, groups, keep, sff, vocab = PUTURAX_SIZES[size]
+    context, pk = args.context, peaks()
+    warmup = max(args.warmup, 3)
+    qwen = dict(QWEN3_8B, num_hidden_layers=layers, hidden_size=W, num_attention_heads=H, num_key_value_heads=KV,
+                head_dim=D, intermediate_size=top * eff + sff, vocab_size=vocab, max_position_embeddings=16384)
+    results = {}
+    for name, cfg in (("puturax", puturax_config(size, layers)), ("qwen3", qwen)):
+        _, plan, weights = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+        slack = 256
+        pages = 64 * (-(-(context + slack) // args.block_size) + 1) + PREFILL_TOKENS // args.block_size + 64
+        engine = LLMEngine(plan=plan, weights=weights, dtype="bfloat16", kv_blocks=pages, block_size=args.block_size,
+                           max_batch_size=64, max_num_batched_tokens=PREFILL_TOKENS, prefill_chunk_size=PREFILL_TOKENS,
+                           max_model_len=context + slack)
+        del weights
+        runner, sampler = engine.runner, engine.sampler
+        for t in runner.storage.paged:
+            t.normal_()
+        res = {}
+        pms = prefill_run(runner, vocab)
+        res["prefill"] = {"tokens": PREFILL_TOKENS, "ms": round(pms, 3), "tokens_per_s": round(PREFILL_TOKENS / pms * 1e3, 1)}
+        for b in (8, 64):
+            ms, launches, _ = decode_run(runner, sampler, b, context, warmup, args.steps, "random", vocab, f"d{b}.")
+            res[f"decode_b{b}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(b * 1e3 / ms, 1), "launches": round(launches)}
+        gen = torch.Generator().manual_seed(5)
+        prompt = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
+        res["kernels_prefill"] = timed_step(runner, [StepEntry("kp", prompt, [PREFILL_TOKENS - 1])])
+        runner.release("kp")
+        ids = [f"kd{i}" for i in range(64)]
+        for rid in ids:
+            runner.cache.admit(rid)
+            runner.cache.append(rid, context - 1)
+        runner.storage.zero_slots(runner.cache.take_fresh_slots())
+        res["kernels_decode_b64"] = timed_step(runner, [StepEntry(rid, [i], [0]) for i, rid in enumerate(ids)])
+        for rid in ids:
+            runner.release(rid)
+        runner.check_device_errors()
+        res["weights_GB"] = round(sum(p.numel() * p.element_size() for p in _tensors_of(runner.model)) / 1e9, 2)
+        results[name] = res
+        del engine, runner, sampler
+        torch.cuda.empty_cache()
+    # ---- the new kernels against their rooflines, beside the like kernels of the closest model ---------
+    T, B = PREFILL_TOKENS, 64
+    px, q = results["puturax"], results["qwen3"]
+    def us(res, step, names):
+        return sum(res[step].get(n, [0, 0.0])[1] for n in names)
+    def count(res, step, name):
+        return res[step].get(name, [0, 0.0])[0]
+    tf = lambda flops, micro: round(flops / (micro * 1e-6) / 1e12, 1) if micro else None
+    gb = lambda nbytes, micro: round(nbytes / (micro * 1e-6) / 1e9, 1) if micro else None
+    n_lat = sum(1 for i in range(layers) if i % 4 == 0)
+    n_par = layers - n_lat
+    att = ("paged_attention", "flash_prefill", "flash_prefill_tc5", "flash_decode")
+    shaped = tuple(a + "+shape" for a in att)
+    keys_all = T * (T + 1) // 2
+    row = -(-(KR + R) // 16) * 16
+    roof = {}
+    roof["attention_prefill_tflops"] = {
+        "puturax capped, distance bias, sink (mma.sync)": tf(n_par * 4.0 * H * D * keys_all, us(px, "kernels_prefill", shaped)),
+        "puturax latent row": tf(n_lat * 4.0 * H * row * keys_all, us(px, "kernels_prefill", att)),
+        "qwen3": tf(layers * 4.0 * H * D * keys_all, us(q, "kernels_prefill", att)),
+        "us_a_layer": {"puturax shaped": round(us(px, "kernels_prefill", shaped) / max(n_par, 1), 1),
+                       "puturax latent": round(us(px, "kernels_prefill", att) / max(n_lat, 1), 1),
+                       "qwen3": round(us(q, "kernels_prefill", att) / layers, 1)}}
+    roof["attention_decode_gbs"] = {
+        "puturax capped, distance bias, sink": gb(n_par * B * context * 2.0 * KV * D * 2.0, us(px, "kernels_decode_b64", shaped)),
+        "puturax latent row": gb(n_lat * B * context * row * 2.0, us(px, "kernels_decode_b64", att)),
+        "qwen3": gb(layers * B * context * 2.0 * KV * D * 2.0, us(q, "kernels_decode_b64", att)),
+        "us_a_layer": {"puturax shaped": round(us(px, "kernels_decode_b64", shaped) / max(n_par, 1), 1),
+                       "puturax latent": round(us(px, "kernels_decode_b64", att) / max(n_lat, 1), 1),
+                       "qwen3": round(us(q, "kernels_decode_b64", att) / layers, 1)}}
+    for step, rows in (("kernels_prefill", T), ("kernels_decode_b64", B)):
+        r = {}
+        # five mixes: the activation in, five rows out
+        r["token_shift_multi_gbs"] = gb(count(px, step, "token_shift_multi") * rows * W * 12.0, us(px, step, ("token_shift_multi",)))
+        # head work: q, k, v in; q, k, v out (bfloat16)
+        r["head_norm_write_gbs"] = gb(count(px, step, "head_norm_write") * rows * (H + 2 * KV) * D * 4.0, us(px, step, ("head_norm_write",)))
+        r["qwen3_qk_norm_rope_write_gbs"] = gb(count(q, step, "qk_norm_rope_write") * rows * (H + 2 * KV) * D * 4.0,
+                                               us(q, step, ("qk_norm_rope_write",)))
+        # the norm after a sub-layer: y in, x in and out; the norm before: x in, h out
+        r["rmsnorm_add_gbs"] = gb(count(px, step, "rmsnorm_add") * rows * W * 10.0, us(px, step, ("rmsnorm_add",)))
+        r["add_rmsnorm_gbs"] = gb(count(px, step, "add_rmsnorm") * rows * W * 6.0, us(px, step, ("add_rmsnorm",)))
+        r["qwen3_add_rmsnorm_gbs"] = gb(count(q, step, "add_rmsnorm") * rows * W * 12.0, us(q, step, ("add_rmsnorm",)))
+        # the output gate: heads in and out, gate in; the memory's norm and gate: float32 in, gate in, out
+        r["sigmoid_gate_gbs"] = gb(rows * 6.0 * (n_par + n_lat) * H * D, us(px, step, ("sigmoid_gate",)))
+        r["gate_norm_gbs"] = gb(count(px, step, "gate_norm") * rows * TH * TD * 8.0, us(px, step, ("gate_norm",)))
+        n, micro = count(px, step, "decay_scan"), us(px, step, ("decay_scan",))
+        state = 8.0 * TH * TD * TD * n * (B if step.endswith("b64") else 1)
+        r["decay_scan"] = {"us_a_layer": round(micro / max(n, 1), 1), "us_a_token_and_layer": round(micro / max(n, 1) / (rows if step == "kernels_prefill" else 1), 3),
+                           "gflops": round(6.0 * TH * TD * TD * rows * n / (micro * 1e-6) / 1e9, 1) if micro else None,
+                           "state_gbs": gb(state, micro)}
+        roof[step] = r
+    grouped = ("gemm_grouped", "gemm_grouped_fused", "gemm_grouped_tc5")
+    q_layer = (H + 2 * KV) * D * W + W * H * D + 3 * W * (top * eff + sff)          # matrix elements of a Qwen3 layer
+    roof["expert_products_prefill_tflops"] = {
+        "puturax": tf(n_par * 2.0 * T * top * 3 * W * eff, us(px, "kernels_prefill", grouped)),
+        "qwen3 (all dense products of the layers)": tf(layers * 2.0 * T * q_layer,
+                                                       us(q, "kernels_prefill", ("gemm_bf16_tc5", "gemm_bf16_tc5_pair", "library_mm")))}
+    touched = min(E, B * top)
+    roof["expert_products_decode_gbs"] = {
+        "puturax (experts that 64 tokens can reach)": gb(n_par * touched * 3.0 * W * eff * 2, us(px, "kernels_decode_b64", grouped)),
+        "qwen3 (all products)": gb(q["weights_GB"] * 1e9 - 2.0 * vocab * W * 2, us(q, "kernels_decode_b64", ("library_mm", "gemm_bf16_small_m")))}
+    roof["peaks"] = {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "source": pk["source"]}
+    print(json.dumps({"puturax_bench": size, "layers": layers, "context": context, "steps": args.steps, "warmup": warmup,
+                      "dtype": "bf16", "data": "synthetic (random weights, uniform token ids)",
+                      "config": {"puturax": dict(zip(("width", "heads", "kv_heads", "dim", "q_rank", "kv_rank", "rot_dim", "mix_heads",
+                                                      "mix_dim", "decay_rank", "dense_ff", "expert_ff", "experts", "top", "groups", "kept",
+                                                      "shared_ff", "vocab"), PUTURAX_SIZES[size])),
+                                 "qwen3": {k_: qwen[k_] for k_ in ("hidden_size", "num_attention_heads", "num_key_value_heads",
+                                                                    "head_dim", "intermediate_size", "vocab_size")}},
+                      "results": results, "roofline": roof}))
+    return 0
+
+
 def _tensors_of(model):
     """Every device tensor that the parts of a model hold (weights as they are resident)."""
     import torch
@@ -891,6 +1036,9 @@ def main(argv=None):
     ap.add_argument("--sodonex", default=None, choices=sorted(SODONEX_SIZES), metavar="SIZE",
                     help="instead of the default workload: the Sodonex decoder at layer sizes " + ", ".join(sorted(SODONEX_SIZES))
                          + " beside the Qwen3 decoder at equal width, depth, heads and active feed-forward width")
+    ap.add_argument("--puturax", default=None, choices=sorted(PUTURAX_SIZES), metavar="SIZE",
+                    help="instead of the default workload: the Puturax decoder at layer sizes " + ", ".join(sorted(PUTURAX_SIZES))
+                         + " beside the Qwen3 decoder at equal width, depth, heads and active feed-forward width")
     ap.add_argument("--kikepel", default=None, choices=sorted(KIKEPEL_SIZES), metavar="SIZE",
                     help="instead of the default workload: the Kikepel decoder at layer sizes " + ", ".join(sorted(KIKEPEL_SIZES))
                          + " beside the Qwen3 decoder at equal width, depth and heads: prefill of 2,048 tokens, decode at batch 8 "
@@ -911,6 +1059,8 @@ def main(argv=None):
         return tuzisun_bench(args)
     if args.sodonex:
         return sodonex_bench(args)
+    if args.puturax:
+        return puturax_bench(args)
     import torch
     from vllm_lite_b200.csrc import ops
     from vllm_lite_b200.engine import LLMEngine, random_model

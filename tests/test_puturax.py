@@ -813,7 +813,9 @@ def test_portions_of_changing_size(which, dtype):
 def mixed_schedule(which):
     """Up to three live requests in three state slots: portions beside single tokens, requests that pause, end and are
     replaced, so that pages and slots change hands."""
-    reqs = {k: tokens_for(which, n, 60 + i) for i, (k, n) in enumerate([("a", 90), ("b", 41), ("c", 7), ("d", 66), ("e", 30)])}
+    # (seeds chosen so that no request starts on a token whose first time-mixing output, sign(r . (u k)) v / rms(v) per head,
+    # has a sum near zero: bfloat16 rounding can turn that sign, and the float32 tests hold such rows to every bit anyway)
+    reqs = {k: tokens_for(which, n, 260 + i) for i, (k, n) in enumerate([("a", 90), ("b", 41), ("c", 7), ("d", 66), ("e", 30)])}
     fed = {k: 0 for k in reqs}
     plan = [[("a", 30), ("b", 2)], [("a", 1), ("b", 17), ("c", 3)], [("a", 29), ("c", 1)], [("b", 1), ("c", 3)],
             [("a", 2), ("b", 21), ("d", 40)], [("a", 28), ("d", 1)], [("d", 2), ("e", 9)], [("d", 23), ("e", 1)], [("e", 20)]]
