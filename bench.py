@@ -431,7 +431,7 @@ TIMED_OPS = ("paged_attention", "flash_prefill", "flash_prefill_tc5", "flash_dec
              "moe_gather", "moe_combine", "gated_act", "silu_mul", "scale_softcap", "embed", "cast", "add_bias",
              "hc_step", "dyt_rows", "short_conv", "ssd_scan", "mlstm_scan", "delta_scan", "gate_norm", "scaled_sum",
              "token_shift", "rows_norm_rope_write", "conv_rows_norm_rope_write", "rmsnorm_add", "unary_act",
-             "head_norm_write", "rope_heads", "sigmoid_gate", "token_shift_multi", "decay_scan")
+             "head_norm_write", "rope_heads", "sigmoid_gate", "token_shift_multi", "decay_scan", "decay_from_raw")
 
 
 def kikepel_config(size, layers):

@@ -430,7 +430,7 @@ def test_memory_with_a_decay_per_key_channel(H_, D_):
     r, k, v = ([rand((n[b], HD + 3), 20 + 5 * i + b, torch.float32, 0.7) for b in (0, 1)] for i in range(3))
     z = [rand((n[b], HD), 40 + b, torch.float32, 1.0) for b in (0, 1)]
     w0, u = rand((HD,), 42, torch.float32, 1.0) - 2.0, rand((HD,), 43)
-    floats = o.scan_state_floats(H_, D_, D_)
+    floats = o.decay_state_floats(H_, D_, D_)
     state = torch.zeros((3, 5 + floats), dtype=torch.float32, device=DEV)
     slots = [1, 2]
 
@@ -438,7 +438,8 @@ def test_memory_with_a_decay_per_key_channel(H_, D_):
         step = mini_step(lens, [slots[b] for b in live], starts)
         cat = lambda xs: torch.cat([xs[b][s:s + c] for b, s, c in zip(live, starts, lens)]).contiguous()
         out = torch.empty((sum(lens), HD), dtype=torch.float32, device=DEV)
-        o.decay_scan((cat(r), 3), (cat(k), 0), (cat(v), 1), (cat(z), 0), w0, u, state, 5, step.cu_seqlens, step.state_slots, out, H_, D_, D_)
+        w = o.decay_from_raw(cat(z), 0, w0)
+        o.decay_scan((cat(r), 3), (cat(k), 0), (cat(v), 1), (w, 0), u, state, 5, step.cu_seqlens, step.state_slots, out, H_, D_, D_)
         return out
 
     got = in_portions(n, fn)

@@ -52,8 +52,9 @@ _SIGNATURES = {
     ("recurrent", "vl_token_shift_multi"): [c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
                                             c_void_p, c_int, c_int, c_int, c_void_p],
     ("recurrent", "vl_decay_scan"): [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
-                                     c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                     c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                      c_int, c_int, c_void_p],
+    ("recurrent", "vl_decay_from_raw"): [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
     ("rope_cache", "vl_conv_rows_norm_rope_write"): [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p,
                                                      c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
                                                      c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
@@ -1487,21 +1488,53 @@ def token_shift_multi(h, mu, state, state_off, cu, slots, req_index, positions, 
     return out
 
 
-def decay_scan(r, k, v, z, w0, u, state, state_off, cu, slots, o, H, D, P):
+DECAY_SCAN_THREADS = 128
+
+
+def decay_scan_shape(D: int, P: int):
+    """(rows a lane, lanes a column, columns a block, blocks a head) of `decay_scan` over a state of D rows and P columns per
+    head; the same arithmetic as csrc/recurrent.cu (decay_shape), on which the state's size rests."""
+    if not 0 < D <= 512 or P <= 0:
+        raise KernelError(f"decay_scan takes states of 1 to 512 rows, got {D} x {P}")
+    rows = 4 if D <= 128 else (8 if D <= 256 else 16)
+    L = 1
+    while L * rows < D:
+        L *= 2
+    ct = DECAY_SCAN_THREADS // L
+    return rows, L, ct, -(-P // ct)
+
+
+def decay_state_floats(H, D, P) -> int:
+    """Floats of `decay_scan`'s state (H heads of D x P numbers) in the layout the kernel keeps it in."""
+    rows, _, _, Z = decay_scan_shape(D, P)
+    return H * Z * rows * DECAY_SCAN_THREADS
+
+
+def decay_from_raw(z, col, w0):
+    """In place on columns col .. col + len(w0) of z [T, ld]: z <- exp(-exp(z + w0)), a decay in (0, 1) per column (float32 inside)."""
+    _need(z, None, "z", 2); _need(w0, torch.float32, "w0", 1)
+    if col < 0 or col + w0.shape[0] > z.shape[1]:
+        raise KernelError("decay_from_raw: the columns leave the rows")
+    _check(_fn("recurrent", "vl_decay_from_raw")(_ptr(z), dtype_code(z.dtype), z.shape[0], z.shape[1], int(col), _ptr(w0),
+                                                 w0.shape[0], _stream()), "vl_decay_from_raw")
+    return z
+
+
+def decay_scan(r, k, v, w, u, state, state_off, cu, slots, o, H, D, P):
     """Per head a memory S [D, P] with a decay per key channel: o_t = (S + diag(u) k_t v_t^T)^T r_t, then
-    S <- diag(exp(-exp(z_t + w0))) S + k_t v_t^T.  r, k, z: (tensor [T, ld], first column) with H*D columns, v likewise
-    with H*P, all of one dtype; w0, u float32 [H*D]; o float32 [T, H*P]; the state as `scan_state_floats(H, D, P)`."""
-    (rt, rc), (kt, kc), (vt, vc), (zt, zc) = r, k, v, z
-    for t, n in ((rt, "r"), (kt, "k"), (vt, "v"), (zt, "z")):
+    S <- diag(w_t) S + k_t v_t^T.  r, k, w: (tensor [T, ld], first column) with H*D columns, v likewise with H*P, all of
+    one dtype; u float32 [H*D] (the bonus of the current token); o float32 [T, H*P]; the state as `decay_state_floats(H, D, P)`."""
+    (rt, rc), (kt, kc), (vt, vc), (wt, wc) = r, k, v, w
+    for t, n in ((rt, "r"), (kt, "k"), (vt, "v"), (wt, "w")):
         _need(t, rt.dtype, n, 2)
-    _need(o, torch.float32, "o", 2); _need(w0, torch.float32, "w0", 1); _need(u, torch.float32, "u", 1)
+    _need(o, torch.float32, "o", 2); _need(u, torch.float32, "u", 1)
     T = rt.shape[0]
-    if kt.shape[0] != T or vt.shape[0] != T or zt.shape[0] != T or o.shape != (T, H * P) or w0.shape[0] != H * D or u.shape[0] != H * D:
+    if kt.shape[0] != T or vt.shape[0] != T or wt.shape[0] != T or o.shape != (T, H * P) or u.shape[0] != H * D:
         raise KernelError("decay_scan: shapes disagree")
     B = _seg_args(cu, slots)
-    sp, stride = _state_args(state, state_off, scan_state_floats(H, D, P))
+    sp, stride = _state_args(state, state_off, decay_state_floats(H, D, P))
     _check(_fn("recurrent", "vl_decay_scan")(_ptr(rt), rt.shape[1], int(rc), _ptr(kt), kt.shape[1], int(kc), _ptr(vt), vt.shape[1],
-                                             int(vc), _ptr(zt), zt.shape[1], int(zc), dtype_code(rt.dtype), _ptr(w0), _ptr(u), sp,
+                                             int(vc), _ptr(wt), wt.shape[1], int(wc), dtype_code(rt.dtype), _ptr(u), sp,
                                              stride, _ptr(cu), _ptr(slots), B, _ptr(o), H, D, P, _stream()), "vl_decay_scan")
     return o
 

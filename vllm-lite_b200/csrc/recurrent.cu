@@ -726,9 +726,11 @@ extern "C" int vl_gate_norm(const float* y, const void* gate, int dtype, int ld,
 // ------------------------------------------------------------------------------------------ several token shifts at once
 // out[s][t] = h[t] + (h[t - 1] - h[t]) * mu[s], s < S: S mixes of a row with the row of the token before, each with its own
 // mu [W] (float32 arithmetic; h and out in the activation dtype, out [S, T, W]).  The row before a portion's first token
-// is the state's row (float32; zeros in a fresh slot), which the block of that token replaces by the portion's last row,
-// as in vl_token_shift.  A row at a negative position passes unchanged into every mix and touches no state.
-template <typename T>
+// is the state's row (float32; zeros in a fresh slot), which the blocks of that token replace by the portion's last row,
+// as in vl_token_shift (a thread reads its elements of the old state before it writes the new ones, and no other thread
+// touches those elements).  A row at a negative position passes unchanged into every mix and touches no state.
+// A thread takes VEC neighbouring elements (4 where every row starts on a 16-byte boundary), a block 256 * VEC of a token.
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256)
 token_shift_multi_kernel(const T* __restrict__ h, const float* __restrict__ mu, int S, float* state, long long state_stride,
                          const int* __restrict__ cu, const int* __restrict__ slots, const int* __restrict__ req_index,
@@ -738,20 +740,48 @@ token_shift_multi_kernel(const T* __restrict__ h, const float* __restrict__ mu, 
     const int b = req_index[t], pos = positions[t];
     const bool live = pos >= 0;
     const int first = live ? cu[b] : 0, last = live ? cu[b + 1] - 1 : 0;
+    const int i = (blockIdx.y * 256 + threadIdx.x) * VEC;
     pdl_wait();
+    if (i >= W) return;
     const T* xr = h + (size_t)t * W;
     const bool head = live && t == first;
-    float* st = live ? state + (long long)slots[b] * state_stride : nullptr;
-    const T* keep = h + (size_t)last * W;
-    for (int i = threadIdx.x; i < W; i += 256) {
-        const float v = to_f32(xr[i]);
-        float p = v;
-        if (live) {
-            if (head) { p = st[i]; st[i] = to_f32(keep[i]); }
-            else p = to_f32(xr[i - W]);
+    float v[VEC], p[VEC];
+    if (VEC == 4) {
+        const float4 a = Quad<T>::load(xr + i);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    } else {
+        v[0] = to_f32(xr[i]);
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) p[e] = v[e];
+    if (head) {
+        float* st = state + (long long)slots[b] * state_stride + i;
+        const T* keep = h + (size_t)last * W + i;
+        if (VEC == 4) {
+            const float4 o = *reinterpret_cast<const float4*>(st), k = Quad<T>::load(keep);
+            p[0] = o.x; p[1] = o.y; p[2] = o.z; p[3] = o.w;
+            *reinterpret_cast<float4*>(st) = k;
+        } else {
+            p[0] = st[0];
+            st[0] = to_f32(keep[0]);
         }
-        for (int s = 0; s < S; ++s)
-            out[((size_t)s * ntok + t) * W + i] = from_f32<T>(v + (p - v) * mu[(size_t)s * W + i]);
+    } else if (live) {
+        if (VEC == 4) {
+            const float4 a = Quad<T>::load(xr - W + i);
+            p[0] = a.x; p[1] = a.y; p[2] = a.z; p[3] = a.w;
+        } else {
+            p[0] = to_f32(xr[i - W]);
+        }
+    }
+    for (int s = 0; s < S; ++s) {
+        T* o = out + ((size_t)s * ntok + t) * W + i;
+        if (VEC == 4) {
+            const float4 m = *reinterpret_cast<const float4*>(mu + (size_t)s * W + i);
+            Quad<T>::store(o, make_float4(v[0] + (p[0] - v[0]) * m.x, v[1] + (p[1] - v[1]) * m.y, v[2] + (p[2] - v[2]) * m.z,
+                                          v[3] + (p[3] - v[3]) * m.w));
+        } else {
+            o[0] = from_f32<T>(v[0] + (p[0] - v[0]) * mu[(size_t)s * W + i]);
+        }
     }
 }
 
@@ -761,92 +791,217 @@ extern "C" int vl_token_shift_multi(const void* h, const float* mu, int S, float
     if (T <= 0) return VL_OK;
     if (W <= 0 || S <= 0 || state_stride < W) return VL_ERR_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == VL_F32)
-        return vl_launch(token_shift_multi_kernel<float>, dim3(T), dim3(256), 0, s, (const float*)h, mu, S, state, state_stride, cu,
-                         slots, req_index, positions, (float*)out, T, W);
-    if (dtype == VL_BF16)
-        return vl_launch(token_shift_multi_kernel<bf16>, dim3(T), dim3(256), 0, s, (const bf16*)h, mu, S, state, state_stride, cu,
-                         slots, req_index, positions, (bf16*)out, T, W);
+    const bool vec = W % 4 == 0 && state_stride % 4 == 0 &&
+                     (((uintptr_t)h | (uintptr_t)mu | (uintptr_t)state | (uintptr_t)out) & 15) == 0;
+    const int per = 256 * (vec ? 4 : 1);
+    const dim3 grid(T, (W + per - 1) / per);
+#define TSM_LAUNCH(TYPE, VEC)                                                                                                \
+    return vl_launch(token_shift_multi_kernel<TYPE, VEC>, grid, dim3(256), 0, s, (const TYPE*)h, mu, S, state, state_stride, \
+                     cu, slots, req_index, positions, (TYPE*)out, T, W)
+    if (dtype == VL_F32) { if (vec) TSM_LAUNCH(float, 4); TSM_LAUNCH(float, 1); }
+    if (dtype == VL_BF16) { if (vec) TSM_LAUNCH(bf16, 4); TSM_LAUNCH(bf16, 1); }
+#undef TSM_LAUNCH
     return VL_ERR_UNSUPPORTED;
 }
 
 // ------------------------------------------------------------------------------------------ memory with a decay per key channel
 // Per head, S [D x P] from the request's state:   o_t = (S + diag(u) k_t v_t^T)^T r_t;   S <- diag(w_t) S + k_t v_t^T
-// with w_t = exp(-exp(z_t + w0)) per key channel (z the raw decay, w0 [H*D]) and u [H*D] a bonus for the current token alone.
-// r, k, z float32 rows with H*D columns from `rc`, `kc`, `zc` on; v float32 with H*P columns.  o float32 [T, H*P].
-// Staged per token: r [D] | k [D] | decay [D] | v [CT]; the two exponentials are taken once per token on the staged values.
-template <typename TP, int ROWS, int L>
-__global__ void __launch_bounds__(RC_MAX_THREADS)
+// with w_t = exp(-exp(z_t + w0)) per key channel and u [H*D] a bonus for the current token alone.
+//
+// vl_decay_from_raw turns the raw decays z [T, ld] (columns zc .. zc + H*D) into w in place, one thread an element: the two
+// exponentials are taken once per token, outside the walk.
+// vl_decay_scan walks the tokens.  r, k, w float32 rows with H*D columns from `rc`, `kc`, `wc` on; v with H*P columns;
+// o float32 [T, H*P].  A block of DS_THREADS threads owns (head, request, tile of DS_THREADS / L value columns); a column of
+// the state lies in the registers of L lanes, lane l holding the ROWS neighbouring rows from ROWS * l on, so that a lane
+// fetches its share of r, k and w of a token with one 16-byte read each (ROWS = 4; 8 and 16 rows: two and four reads).  The
+// vectors of a chunk of tokens are staged in shared memory one chunk ahead, as in the other scans; the walk is unrolled so
+// that the butterfly sums of neighbouring tokens overlap (only `S <- w S + k v` chains from token to token).  Blocks are
+// small (128 threads) so that one request's heads and column tiles spread over every SM.  The state's layout is the
+// kernel's own: [head][column tile][row i of a lane][thread] (vl_decay_state_floats).
+#define DS_THREADS 128
+#define DS_PREFETCH 16
+#define DS_PIECES 4          // most 16-byte pieces of a token that one thread copies: 3 D / 4 + a few, over 128 threads (D <= 160)
+struct DecayShape { int rows, L, CT, Z; };
+static inline bool decay_shape(int D, int P, DecayShape* sh) {
+    if (D <= 0 || P <= 0 || D > 512) return false;
+    sh->rows = D <= 128 ? 4 : (D <= 256 ? 8 : 16);
+    int L = 1;
+    while (L * sh->rows < D) L <<= 1;
+    sh->L = L;
+    sh->CT = DS_THREADS / L;
+    sh->Z = (P + sh->CT - 1) / sh->CT;
+    return true;
+}
+extern "C" long long vl_decay_state_floats(int H, int D, int P) {
+    DecayShape sh;
+    if (H <= 0 || !decay_shape(D, P, &sh)) return -1;
+    return (long long)H * sh.Z * sh.rows * DS_THREADS;
+}
+
+template <typename TP>
+__global__ void decay_from_raw_kernel(TP* __restrict__ z, int ld, int zc, const float* __restrict__ w0, int HD, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (idx >= total) return;
+    const size_t t = idx / HD;
+    const int c = (int)(idx - t * HD);
+    TP* p = z + t * ld + zc + c;
+    *p = from_f32<TP>(expf(-expf(to_f32(*p) + w0[c])));
+}
+
+extern "C" int vl_decay_from_raw(void* z, int dtype, int T, int ld, int zc, const float* w0, int HD, void* stream) {
+    if (T <= 0) return VL_OK;
+    if (HD <= 0 || zc < 0 || zc + HD > ld) return VL_ERR_ARGUMENT;
+    const size_t total = (size_t)T * HD;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VL_F32) return vl_launch(decay_from_raw_kernel<float>, dim3(blocks), dim3(256), 0, s, (float*)z, ld, zc, w0, HD, total);
+    if (dtype == VL_BF16) return vl_launch(decay_from_raw_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (bf16*)z, ld, zc, w0, HD, total);
+    return VL_ERR_UNSUPPORTED;
+}
+
+// FAST (float32 rows whose heads start on 16-byte boundaries): the staging is 16-byte cp.async copies, a token's pieces
+// spread over the block's threads with no division in sight; else every element through a register (any dtype, any size).
+__device__ __forceinline__ void ds_cp_async16(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void ds_cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+template <typename TP, int ROWS, int L, bool FAST>
+__global__ void __launch_bounds__(DS_THREADS)
 decay_scan_kernel(const TP* __restrict__ rp, int ldr, int rc, const TP* __restrict__ kp, int ldk, int kc, const TP* __restrict__ vp,
-                  int ldv, int vc, const TP* __restrict__ zp, int ldz, int zc, const float* __restrict__ w0,
-                  const float* __restrict__ u, float* __restrict__ state, long long state_stride, const int* __restrict__ cu,
-                  const int* __restrict__ slots, float* __restrict__ o, int H, int D, int P, int chunk) {
-    extern __shared__ float sm[];
+                  int ldv, int vc, const TP* __restrict__ wp, int ldw, int wc, const float* __restrict__ u,
+                  float* __restrict__ state, long long state_stride, const int* __restrict__ cu,
+                  const int* __restrict__ slots, float* __restrict__ o, int H, int D, int P, int chunk, int DP) {
+    extern __shared__ __align__(16) float sm[];
     pdl_launch_dependents();
     pdl_wait();
     const int h = blockIdx.x, b = blockIdx.y;
     const int s0 = cu[b], n = cu[b + 1] - s0;
     if (n <= 0) return;
-    const int NT = blockDim.x, CT = NT / L, tid = threadIdx.x;
+    constexpr int NT = DS_THREADS, CT = NT / L;
+    const int tid = threadIdx.x;
     const int col = tid / L, l = tid % L;
     const int p0 = blockIdx.z * CT, p = p0 + col;
     const bool live = p < P;
-    const int VEC = 3 * D + CT;
-    float* S = scan_state<ROWS>(state, state_stride, slots[b], h);
+    const int VEC = 3 * DP + CT;                         // DP: D rounded up to whole lanes (L * ROWS), so that a lane's reads stay inside
+    float* S = state + (long long)slots[b] * state_stride + ((size_t)h * gridDim.z + blockIdx.z) * ROWS * NT + tid;
     float s[ROWS], ub[ROWS];
 #pragma unroll
     for (int i = 0; i < ROWS; ++i) {
         s[i] = S[(size_t)i * NT];
-        const int r = l + L * i;
+        const int r = ROWS * l + i;
         ub[i] = r < D ? u[(size_t)h * D + r] : 0.f;
     }
     auto raw = [&](int row, int e) -> float {
         const size_t t = (size_t)(s0 + row);
-        if (e < D) return to_f32(rp[t * ldr + rc + (size_t)h * D + e]);
-        if (e < 2 * D) return to_f32(kp[t * ldk + kc + (size_t)h * D + (e - D)]);
-        if (e < 3 * D) return to_f32(zp[t * ldz + zc + (size_t)h * D + (e - 2 * D)]);
-        return p0 + (e - 3 * D) < P ? to_f32(vp[t * ldv + vc + (size_t)h * P + p0 + (e - 3 * D)]) : 0.f;
+        const int part = e / DP, r = e - part * DP;
+        if (part == 0) return r < D ? to_f32(rp[t * ldr + rc + (size_t)h * D + r]) : 0.f;
+        if (part == 1) return r < D ? to_f32(kp[t * ldk + kc + (size_t)h * D + r]) : 0.f;
+        if (part == 2) return r < D ? to_f32(wp[t * ldw + wc + (size_t)h * D + r]) : 0.f;
+        return p0 + (e - 3 * DP) < P ? to_f32(vp[t * ldv + vc + (size_t)h * P + p0 + (e - 3 * DP)]) : 0.f;
     };
-    auto finish = [&](float* buf, int m) {
-        for (int idx = tid; idx < m * D; idx += NT) {
-            const int k = idx / D, r = idx - k * D;
-            float* v = buf + (size_t)k * VEC + 2 * D + r;
-            *v = expf(-expf(*v + w0[(size_t)h * D + r]));
+    float pf[DS_PREFETCH];
+    auto prefetch = [&](int first_row, int m) {
+#pragma unroll
+        for (int j = 0; j < DS_PREFETCH; ++j) {
+            const int idx = tid + j * NT;
+            if (idx < m * VEC) {
+                const int k = idx / VEC;
+                pf[j] = raw(first_row + k, idx - k * VEC);
+            }
         }
     };
-    float pf[RC_PREFETCH];
+    auto commit = [&](float* buf, int m) {
+#pragma unroll
+        for (int j = 0; j < DS_PREFETCH; ++j) {
+            const int idx = tid + j * NT;
+            if (idx < m * VEC) buf[idx] = pf[j];
+        }
+    };
+    // (FAST) 16-byte pieces of a token: D/4 of r, of k and of w, then the tile's columns of v that exist
+    const int q4 = D >> 2, vq = (min(P - p0, CT) + 3) >> 2;
+    // which pieces this thread copies for every token (up to DS_PIECES of them): where they start in the request's first
+    // row, how far the next row lies, where they land in a staged token; worked out once, so a token costs an add and a copy
+    const float* psrc[DS_PIECES];
+    int pld[DS_PIECES], pdst[DS_PIECES];
+    if constexpr (FAST) {
+#pragma unroll
+        for (int j = 0; j < DS_PIECES; ++j) {
+            const int e = tid + j * NT;
+            psrc[j] = nullptr; pld[j] = 0; pdst[j] = 0;
+            if (e < q4) {
+                psrc[j] = reinterpret_cast<const float*>(rp) + (size_t)s0 * ldr + rc + (size_t)h * D + 4 * e; pld[j] = ldr; pdst[j] = 4 * e;
+            } else if (e < 2 * q4) {
+                psrc[j] = reinterpret_cast<const float*>(kp) + (size_t)s0 * ldk + kc + (size_t)h * D + 4 * (e - q4); pld[j] = ldk; pdst[j] = DP + 4 * (e - q4);
+            } else if (e < 3 * q4) {
+                psrc[j] = reinterpret_cast<const float*>(wp) + (size_t)s0 * ldw + wc + (size_t)h * D + 4 * (e - 2 * q4); pld[j] = ldw; pdst[j] = 2 * DP + 4 * (e - 2 * q4);
+            } else if (e < 3 * q4 + vq) {
+                psrc[j] = reinterpret_cast<const float*>(vp) + (size_t)s0 * ldv + vc + (size_t)h * P + p0 + 4 * (e - 3 * q4); pld[j] = ldv; pdst[j] = 3 * DP + 4 * (e - 3 * q4);
+            }
+        }
+    }
+    auto stage = [&](float* buf, int first_row, int m_) {
+        if constexpr (FAST) {
+#pragma unroll
+            for (int j = 0; j < DS_PIECES; ++j) {
+                if (psrc[j]) {
+                    const float* src = psrc[j] + (size_t)first_row * pld[j];
+                    float* dst = buf + pdst[j];
+                    for (int k = 0; k < m_; ++k, src += pld[j], dst += VEC) ds_cp_async16(dst, src);
+                }
+            }
+        }
+    };
     int m = min(chunk, n);
-    scan_prefetch(pf, 0, m, VEC, raw);
-    scan_commit(pf, sm, m, VEC);
-    __syncthreads();
-    finish(sm, m);
+    if constexpr (FAST) {
+        for (int i = tid; i < 2 * chunk * VEC; i += NT) sm[i] = 0.f;      // what no copy touches (rows beyond D, columns beyond P) stays zero
+        __syncthreads();
+        stage(sm, 0, m);
+        ds_cp_async_wait_all();
+    } else {
+        prefetch(0, m);
+        commit(sm, m);
+    }
     __syncthreads();
     int cur = 0;
     for (int t0 = 0; t0 < n; t0 += chunk) {
         const int mn = min(chunk, n - t0 - m);
-        if (mn > 0) scan_prefetch(pf, t0 + m, mn, VEC, raw);
+        if (mn > 0) {
+            if constexpr (FAST) stage(sm + (size_t)(cur ^ 1) * chunk * VEC, t0 + m, mn);
+            else prefetch(t0 + m, mn);
+        }
         const float* buf = sm + (size_t)cur * chunk * VEC;
+#pragma unroll 4
         for (int k = 0; k < m; ++k) {
             const float* v = buf + (size_t)k * VEC;
-            const float vj = v[3 * D + col];
-            float acc = 0.f;
+            const float vj = v[3 * DP + col];
+            float rr[ROWS], kk[ROWS], ww[ROWS];
 #pragma unroll
-            for (int i = 0; i < ROWS; ++i) {
-                const int r = l + L * i;
-                if (r < D) {
-                    const float kv = v[D + r] * vj;
-                    acc += v[r] * (s[i] + ub[i] * kv);
-                    s[i] = v[2 * D + r] * s[i] + kv;
-                }
+            for (int i = 0; i < ROWS; i += 4) {
+                const float4 a = *reinterpret_cast<const float4*>(v + ROWS * l + i);
+                const float4 c = *reinterpret_cast<const float4*>(v + DP + ROWS * l + i);
+                const float4 d = *reinterpret_cast<const float4*>(v + 2 * DP + ROWS * l + i);
+                rr[i] = a.x; rr[i + 1] = a.y; rr[i + 2] = a.z; rr[i + 3] = a.w;
+                kk[i] = c.x; kk[i + 1] = c.y; kk[i + 2] = c.z; kk[i + 3] = c.w;
+                ww[i] = d.x; ww[i + 1] = d.y; ww[i + 2] = d.z; ww[i + 3] = d.w;
             }
-            acc = group_sum<L>(acc);
+            float acc0 = 0.f, acc1 = 0.f;                       // two chains of additions, joined before the lanes' sums
+#pragma unroll
+            for (int i = 0; i < ROWS; i += 2) {                 // rows beyond D hold zeros in r, k and w: they add nothing
+                const float kv0 = kk[i] * vj, kv1 = kk[i + 1] * vj;
+                acc0 += rr[i] * (s[i] + ub[i] * kv0);
+                acc1 += rr[i + 1] * (s[i + 1] + ub[i + 1] * kv1);
+                s[i] = ww[i] * s[i] + kv0;
+                s[i + 1] = ww[i + 1] * s[i + 1] + kv1;
+            }
+            const float acc = group_sum<L>(acc0 + acc1);
             if (live && l == 0) o[(size_t)(s0 + t0 + k) * H * P + (size_t)h * P + p] = acc;
         }
         if (mn > 0) {
-            float* nxt = sm + (size_t)(cur ^ 1) * chunk * VEC;
-            scan_commit(pf, nxt, mn, VEC);
-            __syncthreads();
-            finish(nxt, mn);
+            if constexpr (FAST) ds_cp_async_wait_all();
+            else commit(sm + (size_t)(cur ^ 1) * chunk * VEC, mn);
         }
         __syncthreads();
         cur ^= 1;
@@ -857,25 +1012,52 @@ decay_scan_kernel(const TP* __restrict__ rp, int ldr, int rc, const TP* __restri
 }
 
 extern "C" int vl_decay_scan(const void* rp, int ldr, int rc, const void* kp, int ldk, int kc, const void* vp, int ldv, int vc,
-                             const void* zp, int ldz, int zc, int dtype, const float* w0, const float* u, float* state,
+                             const void* wp, int ldw, int wc, int dtype, const float* u, float* state,
                              long long state_stride, const int* cu, const int* slots, int B, float* o, int H, int D, int P,
                              void* stream) {
     if (B <= 0) return VL_OK;
-    if (H <= 0 || D <= 0 || P <= 0 || rc < 0 || kc < 0 || vc < 0 || zc < 0 || rc + H * D > ldr || kc + H * D > ldk ||
-        vc + H * P > ldv || zc + H * D > ldz)
+    if (H <= 0 || D <= 0 || P <= 0 || rc < 0 || kc < 0 || vc < 0 || wc < 0 || rc + H * D > ldr || kc + H * D > ldk ||
+        vc + H * P > ldv || wc + H * D > ldw)
         return VL_ERR_ARGUMENT;
-    ScanShape sh;
-    if (!scan_shape(D, P, &sh)) return VL_ERR_UNSUPPORTED;
-    const int CT = sh.CT, VEC = 3 * D + CT, chunk = scan_chunk(VEC, sh.threads);
-    if (!chunk) return VL_ERR_UNSUPPORTED;
+    DecayShape sh;
+    if (!decay_shape(D, P, &sh)) return VL_ERR_UNSUPPORTED;
+    const int DP = sh.L * sh.rows, VEC = 3 * DP + sh.CT;
+    // float32 rows whose heads and column tiles start on 16-byte boundaries are staged by 16-byte asynchronous copies
+    const bool fast = dtype == VL_F32 && D % 4 == 0 && P % 4 == 0 && ldr % 4 == 0 && ldk % 4 == 0 && ldv % 4 == 0 && ldw % 4 == 0 &&
+                      rc % 4 == 0 && kc % 4 == 0 && vc % 4 == 0 && wc % 4 == 0 && sh.CT % 4 == 0 &&
+                      3 * (D / 4) + sh.CT / 4 <= DS_PIECES * DS_THREADS &&
+                      (((uintptr_t)rp | (uintptr_t)kp | (uintptr_t)vp | (uintptr_t)wp) & 15) == 0;
+    int chunk = fast ? 16 : DS_PREFETCH * DS_THREADS / VEC;
+    chunk = chunk > 16 ? 16 : chunk;
+    if (chunk < 1) return VL_ERR_UNSUPPORTED;
     dim3 grid(H, B, sh.Z);
     const size_t smem = sizeof(float) * (size_t)2 * chunk * VEC;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == VL_F32)
-        SCAN_LAUNCH(decay_scan_kernel, float, sh, grid, smem, s, (const float*)rp, ldr, rc, (const float*)kp, ldk, kc,
-                    (const float*)vp, ldv, vc, (const float*)zp, ldz, zc, w0, u, state, state_stride, cu, slots, o, H, D, P, chunk);
-    if (dtype == VL_BF16)
-        SCAN_LAUNCH(decay_scan_kernel, bf16, sh, grid, smem, s, (const bf16*)rp, ldr, rc, (const bf16*)kp, ldk, kc,
-                    (const bf16*)vp, ldv, vc, (const bf16*)zp, ldz, zc, w0, u, state, state_stride, cu, slots, o, H, D, P, chunk);
+#define DS_LAUNCH1(TP, RR, LL, FF)                                                                                              \
+    return vl_launch(decay_scan_kernel<TP, RR, LL, FF>, grid, dim3(DS_THREADS), smem, s, (const TP*)rp, ldr, rc, (const TP*)kp, \
+                     ldk, kc, (const TP*)vp, ldv, vc, (const TP*)wp, ldw, wc, u, state, state_stride, cu, slots, o, H, D, P, chunk, DP)
+#define DS_LAUNCH(TP, RR, LL)            \
+    do {                                 \
+        if (fast) DS_LAUNCH1(TP, RR, LL, true); \
+        DS_LAUNCH1(TP, RR, LL, false);   \
+    } while (0)
+#define DS_PICK(TP)                                                                  \
+    do {                                                                             \
+        if (sh.rows == 16) DS_LAUNCH(TP, 16, 32);                                    \
+        if (sh.rows == 8) DS_LAUNCH(TP, 8, 32);                                      \
+        switch (sh.L) {                                                              \
+            case 32: DS_LAUNCH(TP, 4, 32);                                           \
+            case 16: DS_LAUNCH(TP, 4, 16);                                           \
+            case 8: DS_LAUNCH(TP, 4, 8);                                             \
+            case 4: DS_LAUNCH(TP, 4, 4);                                             \
+            case 2: DS_LAUNCH(TP, 4, 2);                                             \
+            default: DS_LAUNCH(TP, 4, 1);                                            \
+        }                                                                            \
+    } while (0)
+    if (dtype == VL_F32) DS_PICK(float);
+    if (dtype == VL_BF16) DS_PICK(bf16);
+#undef DS_PICK
+#undef DS_LAUNCH
+#undef DS_LAUNCH1
     return VL_ERR_UNSUPPORTED;
 }

@@ -185,8 +185,8 @@ class DeltaRule:
 class TimeMix:
     """A memory per head with a decay per key channel, read through five token shifts of the input (`TimeMixSpec`).
 
-    token shifts (one kernel, five mixes) -> W_r, W_k, W_v, W_g, W_w1 each on its own mix -> tanh -> W_w2 -> the scan
-    (`ops.decay_scan`: decays exp(-exp(z + w0)) and the bonus u for the current token inside it) -> RMS norm per head,
+    token shifts (one kernel, five mixes) -> W_r, W_k, W_v, W_g, W_w1 each on its own mix -> tanh -> W_w2 -> the decays
+    exp(-exp(z + w0)) in place (`ops.decay_from_raw`) -> the scan (`ops.decay_scan`) -> RMS norm per head,
     weight, silu gate (`ops.gate_norm`) -> W_o.  The state of a request is one row of float32: the input row of its last
     token, then the heads' memories in the scan's own layout.  r, k, v and the raw decay leave their products in float32
     (the products add in float32 anyway), so nothing that enters the recurrence is rounded to the model's dtype."""
@@ -207,13 +207,13 @@ class TimeMix:
     @staticmethod
     def cache_need(s: TimeMixSpec):
         from ..csrc import ops
-        return FixedState((s.hidden_size + ops.scan_state_floats(s.num_heads, s.dim, s.dim),))
+        return FixedState((s.hidden_size + ops.decay_state_floats(s.num_heads, s.dim, s.dim),))
 
     def __init__(self, s: TimeMixSpec, weights: dict, ctx):
         from ..csrc import ops
         if s.num_heads <= 0 or s.dim <= 0 or s.decay_rank <= 0:
             raise ValueError(f"time mix: {s.num_heads} heads of {s.dim}, decay rank {s.decay_rank}")
-        ops.scan_lanes(s.dim)
+        ops.decay_scan_shape(s.dim, s.dim)
         self.spec, self.dtype = s, ctx.dtype
         mu, r, k, v, g, w1, w2, w0, u, norm, o = s.names
         self.mu = _f32(torch.stack([weights[mu + m] for m in self.MIXES]), ctx)          # [5, W]
@@ -237,10 +237,9 @@ class TimeMix:
         g = self.g(mixes[3], step, "tm.g")
         low = self.w1(mixes[4], step, "tm.w1")
         low = ops.unary_act(low, ws.get(tag + "tm.w1t", tuple(low.shape), low.dtype), "tanh")
-        z = self.w2(low, step, "tm.w2", out_dtype=f32)
+        w = ops.decay_from_raw(self.w2(low, step, "tm.w2", out_dtype=f32), 0, self.w0)
         o = ws.get(tag + "tm.o", (T, H * D), f32)
-        ops.decay_scan((r, 0), (k, 0), (v, 0), (z, 0), self.w0, self.u, cache.state, W, step.cu_seqlens, step.state_slots, o,
-                       H, D, D)
+        ops.decay_scan((r, 0), (k, 0), (v, 0), (w, 0), self.u, cache.state, W, step.cu_seqlens, step.state_slots, o, H, D, D)
         gated = ws.get(tag + "tm.gated", (T, H * D), self.dtype)
         ops.gate_norm(o, g, 0, "silu", False, self.norm, s.eps, gated, D)
         return self.o_proj(gated, step, "tm.out")
