@@ -643,6 +643,32 @@ def test_tensor_core_kernels_take_the_cap_the_distance_bias_and_the_sink(H_, G_,
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("cap,dist,sink", [(4.0, True, True), (0.0, True, False), (2.5, False, True)])
+@pytest.mark.parametrize("H_,G_,D_,page", [(4, 2, 64, 16), (2, 1, 128, 64), (2, 2, 128, 16), (8, 2, 64, 32), (3, 3, 64, 64)])
+def test_tcgen05_prompt_kernel_takes_the_cap_the_distance_bias_and_the_sink(H_, G_, D_, page, cap, dist, sink):
+    """Tiles of 128 query rows of two requests' portions on the tcgen05 kernel, a portion that starts in the middle of a page
+    and a tile that is not full, against the plain sums and the kernel that serves float32."""
+    dtype = torch.bfloat16
+    lens, new = [700, 300], [300, 129]
+    scale = 2.0 * D_ ** -0.5
+    seqs, kc, vc, table, req, pos, q, r1, r2 = shaped_case(dtype, H_, G_, D_, page, lens, new, seed=9)
+    T = len(req)
+    e = torch.zeros(1, dtype=torch.int32, device=DEV)
+    sinks = torch.zeros(H_, device=DEV) if sink else None
+    shape = dict(softcap=cap or None, distance=(r1, r2) if dist else None)
+    ref = torch.empty((T, H_ * D_), dtype=dtype, device=DEV)
+    ops().paged_attention(q, ref, kc, vc, table, ints(req), ints(pos), H_, G_, D_, scale, None, e, sinks=sinks, **shape)
+    tiles = torch.tensor([[0, 0, 128, 400], [0, 128, 128, 528], [0, 256, 44, 656], [1, 300, 128, 171], [1, 428, 1, 299]],
+                         dtype=torch.int32, device=DEV)
+    out = torch.full((T, H_ * D_), float("nan"), dtype=dtype, device=DEV)
+    ops().flash_prefill_tc5(q, out, kc, vc, table, tiles, H_, G_, D_, scale, None, e, sinks=sinks, **shape)
+    assert int(e.item()) == 0
+    close(out, ref, dtype, "against the float32 kernel", tol=1.5e-2)
+    check_shaped(out, seqs, lens, new, req, q, H_, D_, scale, cap, r1 if dist else None, r2 if dist else None, sink, dtype,
+                 "shaped attention on tcgen05", 1.5e-2)
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("E,top,groups,keep", [(8, 2, 4, 2), (16, 4, 4, 3), (6, 6, 1, 1), (6, 1, 6, 1), (12, 3, 3, 2), (5, 2, 5, 3), (9, 3, 3, 1)])
 def test_choice_by_score_plus_correction_within_the_best_groups(E, top, groups, keep):
     """Negative corrections (every choice score below zero: a masked expert must count as minus infinity, not 0), groups

@@ -25,6 +25,7 @@
 // partial results of chunks and warps simply add up (they travel with a maximum of 0, so every merge weighs them 1).
 // Rows of shared-memory tiles are padded by 16 bytes, which makes every 8-row ldmatrix access
 // hit 8 different banks groups for any head size.
+#include "score_shape.cuh"
 #include "rope_head.cuh"
 
 #ifndef FA_HD
@@ -82,23 +83,6 @@ struct AttnOptions {
     float cap_l2;                                        // a bound on the scores, times log2 e (0: none): s <- cap tanh(s / cap)
     const float* dist_a; const float* dist_b;            // per query head (or null): a ln(1 + b (i - j)) is taken off the score
 };
-// A score y (already scaled, in units of log2) bounded by cap_l2 and less the bias of a key `dist` positions back, still in
-// units of log2: cap tanh(y / cap), tanh(z) = 1 - 2 / (1 + e^(2z)); a ln(1 + b d) log2 e = a log2(1 + b d).
-__device__ __forceinline__ float shape_score(float y, float cap_l2, float two_over_cap, float da, float db, int dist) {
-    if (cap_l2 > 0.f) {
-        float r;
-        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + exp2_mufu(y * two_over_cap)));
-        y = cap_l2 - 2.f * cap_l2 * r;
-    }
-    if (da != 0.f) {
-        float l;
-        asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(l) : "f"(fmaf(db, (float)dist, 1.f)));
-        y -= da * l;
-    }
-    return y;
-}
-// 2 log2(e) / cap_l2: what a score in units of log2 is multiplied by to give the exponent of 2 that is e^(2 s / cap)
-__device__ __forceinline__ float two_over_cap(float cap_l2) { return cap_l2 > 0.f ? 2.f * 1.4426950408889634f / cap_l2 : 0.f; }
 __device__ __forceinline__ float gate_factor(const AttnOptions& op, int tok, int h) {
     return op.gate ? 1.f / (1.f + __expf(-__bfloat162float(op.gate[(size_t)tok * op.gate_stride + h]))) : 1.f;
 }

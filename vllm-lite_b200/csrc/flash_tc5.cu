@@ -37,6 +37,7 @@
 // nothing is divided; `gate` multiplies head h's output for token t by sigmoid(gate[t * gate_stride + h]).
 // Every wait on an mbarrier is bounded; when one expires the block records VL_DEV_WAIT_EXPIRED,
 // stops, and still frees its TMEM.
+#include "score_shape.cuh"
 #include "tc5.cuh"
 
 #ifndef FA_HD
@@ -117,7 +118,7 @@ __device__ __forceinline__ unsigned swizzled(int row, int chunk) {
 
 // tiles[i] = {row of the block table, index of the tile's first token in the step, tokens (<= 128),
 // position of the first}
-template <bool SIG>
+template <bool SIG, bool SHAPED>
 __global__ void __launch_bounds__(NTHREADS, 2)
 flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                  const __grid_constant__ CUtensorMap pages_k, const __grid_constant__ CUtensorMap pages_v, int use_pages,
@@ -125,7 +126,8 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                  const int* __restrict__ block_table, int max_blocks, const int4* __restrict__ tiles, int num_tiles,
                  int nq, int nkv, int page_size, int num_pages, float scale_log2, int window, unsigned* err,
                  const float* __restrict__ sinks, int mask_block, const float* __restrict__ head_bias,
-                 const bf16* __restrict__ gate, int gate_stride) {
+                 const bf16* __restrict__ gate, int gate_stride, float cap_l2, const float* __restrict__ dist_a,
+                 const float* __restrict__ dist_b) {
     // tiles of the 128-byte swizzle must start on 1024-byte boundaries; there is no static shared
     // memory in this kernel, so the array starts the block's window
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -323,7 +325,12 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
         int warp_first = window > 0 ? pos0 + warp * 32 + 31 - window + 1 : 0;
         if (mask_block > 0) warp_first = max(warp_first, (pos0 + warp * 32 + 31) / mask_block * mask_block);
         const float bias_log2 = (SIG && head_bias) ? head_bias[h] * 1.4426950408889634f : 0.f;
-        const unsigned masked = (SIG && scale_log2 < 0.f) ? 0x7f800000u : 0xff800000u;   // times the scale: -inf
+        // scores that are bounded or lose the bias of the distance are shaped as they leave tensor memory (csrc/score_shape.cuh)
+        // and are in units of log2 from then on
+        // (SHAPED is a kernel of its own, so that the plain kernels keep their registers)
+        const float sl2 = SHAPED ? 1.f : scale_log2;
+        const float toc = two_over_cap(cap_l2), da = dist_a ? dist_a[h] : 0.f, db = dist_a ? dist_b[h] : 0.f;
+        const unsigned masked = (SIG && sl2 < 0.f) ? 0x7f800000u : 0xff800000u;   // times the scale: -inf
         const unsigned lane_base = (unsigned)(warp * 32) << 16;
         float m = -INFINITY, l = 0.f;
         bool ok = true;
@@ -338,6 +345,11 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             tc5_fence_before();
             mbar_arrive(&s_free[s]);                             // the scores are in registers: the buffer may be written again
             const int j0 = (jt0 + it) * BN;
+            if constexpr (SHAPED) {
+#pragma unroll
+                for (int c = 0; c < BN; ++c)
+                    sv[c] = __float_as_uint(shape_score(__uint_as_float(sv[c]) * scale_log2, cap_l2, toc, da, db, qpos - (j0 + c)));
+            }
             // (warp-uniform) does any row of this warp see a key of the tile that it must not read?
             const bool edge = (j0 + BN - 1 > pos0 + warp * 32) || j0 < warp_first;
             float mx = -INFINITY;
@@ -352,17 +364,17 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             if constexpr (SIG) {
 #pragma unroll
                 for (int c = 0; c < BN; c += 2)
-                    pk[c >> 1] = pack_bf16(sigmoid_log2(fmaf(__uint_as_float(sv[c]), scale_log2, bias_log2)),
-                                           sigmoid_log2(fmaf(__uint_as_float(sv[c + 1]), scale_log2, bias_log2)));
+                    pk[c >> 1] = pack_bf16(sigmoid_log2(fmaf(__uint_as_float(sv[c]), sl2, bias_log2)),
+                                           sigmoid_log2(fmaf(__uint_as_float(sv[c + 1]), sl2, bias_log2)));
             } else {
 #pragma unroll
                 for (int c = 0; c < BN; c += 2) mx = max3(mx, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]));
-                const float m_new = fmaxf(m, mx * scale_log2);       // the scale is positive
+                const float m_new = fmaxf(m, mx * sl2);              // the scale is positive
                 bump = (m_new - m) > RESCALE_ABOVE;                  // false when both are -inf (NaN compares false)
                 corr = bump ? exp2_mufu(m - m_new) : 1.0f;
                 if (bump) m = m_new;
                 const float base = (m == -INFINITY) ? 0.f : m;
-                const unsigned long long scale2 = pair(scale_log2, scale_log2), nbase2 = pair(-base, -base);
+                const unsigned long long scale2 = pair(sl2, sl2), nbase2 = pair(-base, -base);
                 unsigned long long sum2 = pair(0.f, 0.f);
 #pragma unroll
                 for (int c = 0; c < BN; c += 2) {
@@ -446,9 +458,11 @@ extern "C" int vl_flash_prefill_tc5(const void* q, int q_stride, void* out, cons
                                     const int* block_table, int max_blocks, const int* tiles, int num_tiles,
                                     int nq, int nkv, int hd, int page_size, int num_pages, float scale, int window,
                                     unsigned* err, const float* sinks, int weighting, int mask_block, const float* head_bias,
-                                    const void* gate, int gate_stride, void* stream) {
+                                    const void* gate, int gate_stride, float softcap, const float* dist_a, const float* dist_b,
+                                    void* stream) {
     if (num_tiles <= 0) return VL_OK;
     if (hd != HD) return VL_ERR_UNSUPPORTED;
+    if (softcap < 0.f || (dist_a == nullptr) != (dist_b == nullptr)) return VL_ERR_ARGUMENT;
     if (weighting < 0 || weighting > 1 || mask_block < 0 || (gate && gate_stride < nq) || (weighting == 1 && sinks)) return VL_ERR_ARGUMENT;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || num_pages <= 0) return VL_ERR_ARGUMENT;
     if (page_size % 8 || (page_size < BN ? BN % page_size : page_size % BN)) return VL_ERR_UNSUPPORTED;
@@ -471,11 +485,13 @@ extern "C" int vl_flash_prefill_tc5(const void* q, int q_stride, void* out, cons
         rc = tc5_make_map_pages(&pages_v, vcache, num_pages, nkv, page_size, HD, BN / page_size);
         if (rc) return rc;
     }
-    auto kernel = weighting == 1 ? flash_tc5_kernel<true> : flash_tc5_kernel<false>;
+    const bool shaped = softcap > 0.f || dist_a != nullptr;
+    auto kernel = weighting == 1 ? (shaped ? flash_tc5_kernel<true, true> : flash_tc5_kernel<true, false>)
+                                 : (shaped ? flash_tc5_kernel<false, true> : flash_tc5_kernel<false, false>);
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     return vl_launch(kernel, dim3(nq, num_tiles), dim3(NTHREADS), SMEM_BYTES, (cudaStream_t)stream,
                      map_k, map_v, pages_k, pages_v, use_pages, (const bf16*)q, q_stride, (bf16*)out, block_table, max_blocks, (const int4*)tiles,
                      num_tiles, nq, nkv, page_size, num_pages, scale * 1.4426950408889634f, window, err, sinks, mask_block,
-                     head_bias, (const bf16*)gate, gate_stride);
+                     head_bias, (const bf16*)gate, gate_stride, softcap * 1.4426950408889634f, dist_a, dist_b);
 }

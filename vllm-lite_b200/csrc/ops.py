@@ -75,7 +75,7 @@ _SIGNATURES = {
                                          c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p],
     ("flash_tc5", "vl_flash_prefill_tc5"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                             c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
-                                            c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
+                                            c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p],
     ("flash_attn", "vl_flash_decode"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
                                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -601,9 +601,11 @@ def flash_tc5_supported(dtype, head_dim, page_size) -> bool:
 
 
 def flash_prefill_tc5(qkv, out, k_cache, v_cache, block_table, tiles, num_heads, num_kv_heads, head_dim, scale, window, err,
-                      sinks=None, weighting="softmax", mask_chunk=None, head_bias=None, gate=None):
+                      sinks=None, weighting="softmax", mask_chunk=None, head_bias=None, gate=None, softcap=None, distance=None):
     """Attention for prompt portions on the tcgen05 tensor cores; `tiles` as for `flash_prefill`,
-    up to 128 tokens each.  `weighting`, `mask_chunk` (the `chunk` there), `head_bias`, `gate`: see `_check_variant`."""
+    up to 128 tokens each.  `weighting`, `mask_chunk` (the `chunk` there), `head_bias`, `gate`: see `_check_variant`;
+    `softcap`, `distance`: see `_check_score_shape`."""
+    cap, dist_a, dist_b = _check_score_shape(num_heads, softcap, distance)
     _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, head_dim)
     _need(out, torch.bfloat16, "out", 2); _need(tiles, torch.int32, "tiles", 2)
     _check_sinks(sinks, num_heads)
@@ -616,7 +618,7 @@ def flash_prefill_tc5(qkv, out, k_cache, v_cache, block_table, tiles, num_heads,
         _ptr(qkv), qkv.shape[1], _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
         _ptr(tiles), tiles.shape[0], num_heads, num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0],
         float(scale), int(window or 0), _ptr(err), _ptr(sinks), mode, mask_chunk, _ptr(head_bias), _ptr(gate), gate_stride,
-        _stream()), "vl_flash_prefill_tc5")
+        cap, _ptr(dist_a), _ptr(dist_b), _stream()), "vl_flash_prefill_tc5")
     return out
 
 

@@ -138,8 +138,9 @@ def _run_variant(ops, q, out, cache, group, step, spec, scale, weighting, chunk,
 
 
 def _run_shaped(ops, q, out, cache, group, step, spec, scale, sinks, weighting, chunk, head_bias, gate, softcap, distance):
-    """Attention whose scores are capped or lose a bias that grows with the distance: in bfloat16 the mma.sync kernel for
-    portions of prompts and the block-per-chunk kernel for single tokens (a mixed step launches both); in float32, for
+    """Attention whose scores are capped or lose a bias that grows with the distance: in bfloat16 the tensor-core kernels
+    for portions of prompts (tcgen05 for long portions of heads of 64 or 128, else mma.sync) and the block-per-chunk kernel
+    for single tokens (a mixed step launches both); in float32, for
     other head sizes, or together with another weighting, a chunked mask or a gate per head, the one kernel whose sums
     depend on positions alone."""
     shape = dict(softcap=softcap, distance=distance)
@@ -150,8 +151,12 @@ def _run_shaped(ops, q, out, cache, group, step, spec, scale, sinks, weighting, 
         if step.max_query_len == 1:
             return _decode(ops, args, step, spec, group, q.shape[0], group.max_context, sinks=sinks, shape=shape)
         if step.query_tiles is not None:
-            ops.flash_prefill(q, out, cache.k, cache.v, group.block_table, step.query_tiles, spec.num_heads, spec.num_kv_heads,
-                              spec.head_dim, scale, spec.window, step.err, tile_rows=QUERY_TILE, sinks=sinks, **shape)
+            tile_args = (q, out, cache.k, cache.v, group.block_table, step.query_tiles, spec.num_heads, spec.num_kv_heads,
+                         spec.head_dim, scale, spec.window, step.err)
+            if step.max_query_len > 64 and ops.flash_tc5_supported(q.dtype, spec.head_dim, group.page_size):
+                ops.flash_prefill_tc5(*tile_args, sinks=sinks, **shape)
+            else:
+                ops.flash_prefill(*tile_args, tile_rows=QUERY_TILE, sinks=sinks, **shape)
             if step.single_tokens is not None:
                 _decode(ops, args, step, spec, group, step.single_tokens.shape[0], step.single_context,
                         token_index=step.single_tokens, sinks=sinks, shape=shape)
