@@ -420,14 +420,16 @@ def test_five_token_shifts_keep_the_row_before(dtype, W, pad):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("H_,D_", [(2, 16), (3, 12), (1, 64), (4, 32), (2, 128), (1, 200)])
-def test_memory_with_a_decay_per_key_channel(H_, D_):
+@pytest.mark.parametrize("H_,D_,pad", [(2, 16, 3), (3, 12, 3), (1, 64, 3), (4, 32, 0), (2, 128, 0), (1, 200, 4), (2, 64, 8), (1, 512, 0)])
+def test_memory_with_a_decay_per_key_channel(H_, D_, pad):
     """The scan alone: states carried over portions and single tokens, in slots used in another order, against the plain
     recurrence; decays between 0.2 and 1, a bonus for the current token."""
     o = ops()
     n = [13, 6]
     HD = H_ * D_
-    r, k, v = ([rand((n[b], HD + 3), 20 + 5 * i + b, torch.float32, 0.7) for b in (0, 1)] for i in range(3))
+    # (pad: the first column of r inside its rows; 0, 4, 8 keep the rows on 16-byte boundaries, which the staging by
+    # asynchronous copies needs; 3 sends every element through a register)
+    r, k, v = ([rand((n[b], HD + 2 * pad + 4), 20 + 5 * i + b, torch.float32, 0.7) for b in (0, 1)] for i in range(3))
     z = [rand((n[b], HD), 40 + b, torch.float32, 1.0) for b in (0, 1)]
     w0, u = rand((HD,), 42, torch.float32, 1.0) - 2.0, rand((HD,), 43)
     floats = o.decay_state_floats(H_, D_, D_)
@@ -439,13 +441,14 @@ def test_memory_with_a_decay_per_key_channel(H_, D_):
         cat = lambda xs: torch.cat([xs[b][s:s + c] for b, s, c in zip(live, starts, lens)]).contiguous()
         out = torch.empty((sum(lens), HD), dtype=torch.float32, device=DEV)
         w = o.decay_from_raw(cat(z), 0, w0)
-        o.decay_scan((cat(r), 3), (cat(k), 0), (cat(v), 1), (w, 0), u, state, 5, step.cu_seqlens, step.state_slots, out, H_, D_, D_)
+        o.decay_scan((cat(r), pad), (cat(k), 0), (cat(v), 4 if pad != 3 else 1), (w, 0), u, state, 5, step.cu_seqlens, step.state_slots, out, H_, D_, D_)
         return out
 
     got = in_portions(n, fn)
     for b in (0, 1):
         dec = torch.exp(-torch.exp(z[b].double().cpu() + w0.double().cpu())).view(-1, H_, D_)
-        rr, kk, vv = r[b][:, 3:3 + HD], k[b][:, :HD], v[b][:, 1:1 + HD]
+        vc = 4 if pad != 3 else 1
+        rr, kk, vv = r[b][:, pad:pad + HD], k[b][:, :HD], v[b][:, vc:vc + HD]
         want = torch.stack([P.decayed_memory(rr.double().cpu().view(-1, H_, D_)[:, a], kk.double().cpu().view(-1, H_, D_)[:, a],
                                              vv.double().cpu().view(-1, H_, D_)[:, a], dec[:, a], u.double().cpu().view(H_, D_)[a])
                             for a in range(H_)], 1).reshape(-1, HD)

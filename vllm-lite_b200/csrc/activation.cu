@@ -136,25 +136,39 @@ extern "C" int vl_gated_act(const void* gu, void* out, int dtype, int T, int I, 
 
 // A function of one argument, element by element in float32: act 16 = the square of max(v, 0), 17 = tanh(v) (the codes
 // continue those of the gated activations, which take two).
-template <typename T>
+__device__ __forceinline__ float unary_value(float v, int act) {
+    if (act == 16) { v = fmaxf(v, 0.f); return v * v; }
+    return act == 17 ? tanhf(v) : v;
+}
+// VEC = 4: a thread takes four neighbouring values (one 16- or 8-byte access each way), when the buffers allow it.
+template <typename T, int VEC>
 __global__ void unary_act_kernel(const T* __restrict__ in, T* __restrict__ out, size_t n, int act) {
     pdl_launch_dependents();
     pdl_wait();
-    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    const size_t i = ((size_t)blockIdx.x * 256 + threadIdx.x) * VEC;
     if (i >= n) return;
-    float v = to_f32(in[i]);
-    if (act == 16) { v = fmaxf(v, 0.f); v = v * v; }
-    else if (act == 17) v = tanhf(v);
-    out[i] = from_f32<T>(v);
+    if (VEC == 4) {
+        const float4 v = Quad<T>::load(in + i);
+        Quad<T>::store(out + i, make_float4(unary_value(v.x, act), unary_value(v.y, act), unary_value(v.z, act), unary_value(v.w, act)));
+    } else {
+        out[i] = from_f32<T>(unary_value(to_f32(in[i]), act));
+    }
 }
 
 extern "C" int vl_unary_act(const void* in, void* out, int dtype, long long n, int act, void* stream) {
     if (n <= 0) return VL_OK;
     if (act != 16 && act != 17) return VL_ERR_ARGUMENT;
-    const unsigned blocks = (unsigned)((n + 255) / 256);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == VL_F32) return vl_launch(unary_act_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)in, (float*)out, (size_t)n, act);
-    if (dtype == VL_BF16) return vl_launch(unary_act_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (const bf16*)in, (bf16*)out, (size_t)n, act);
+    const bool vec = n % 4 == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0;
+    const unsigned blocks = (unsigned)((n / (vec ? 4 : 1) + 255) / 256);
+    if (dtype == VL_F32) {
+        if (vec) return vl_launch(unary_act_kernel<float, 4>, dim3(blocks), dim3(256), 0, s, (const float*)in, (float*)out, (size_t)n, act);
+        return vl_launch(unary_act_kernel<float, 1>, dim3(blocks), dim3(256), 0, s, (const float*)in, (float*)out, (size_t)n, act);
+    }
+    if (dtype == VL_BF16) {
+        if (vec) return vl_launch(unary_act_kernel<bf16, 4>, dim3(blocks), dim3(256), 0, s, (const bf16*)in, (bf16*)out, (size_t)n, act);
+        return vl_launch(unary_act_kernel<bf16, 1>, dim3(blocks), dim3(256), 0, s, (const bf16*)in, (bf16*)out, (size_t)n, act);
+    }
     return VL_ERR_UNSUPPORTED;
 }
 
@@ -176,47 +190,71 @@ extern "C" int vl_scale_softcap(float* z, long long n, float scale, float cap, v
 }
 
 // out = sa * a + sb * b: what two mixers that run side by side on one input leave (float32 arithmetic).
-template <typename T>
+template <typename T, int VEC>
 __global__ void scaled_sum_kernel(const T* __restrict__ a, float sa, const T* __restrict__ b, float sb, T* __restrict__ out, size_t n) {
     pdl_launch_dependents();
     pdl_wait();
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) out[i] = from_f32<T>(sa * to_f32(a[i]) + sb * to_f32(b[i]));
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+    if (i >= n) return;
+    if (VEC == 4) {
+        const float4 x = Quad<T>::load(a + i), y = Quad<T>::load(b + i);
+        Quad<T>::store(out + i, make_float4(sa * x.x + sb * y.x, sa * x.y + sb * y.y, sa * x.z + sb * y.z, sa * x.w + sb * y.w));
+    } else {
+        out[i] = from_f32<T>(sa * to_f32(a[i]) + sb * to_f32(b[i]));
+    }
 }
 
 extern "C" int vl_scaled_sum(const void* a, float sa, const void* b, float sb, void* out, int dtype, long long n, void* stream) {
     if (n <= 0) return VL_OK;
-    const unsigned blocks = (unsigned)((n + 255) / 256);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == VL_F32)
-        return vl_launch(scaled_sum_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)a, sa, (const float*)b, sb, (float*)out, (size_t)n);
-    if (dtype == VL_BF16)
-        return vl_launch(scaled_sum_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (const bf16*)a, sa, (const bf16*)b, sb, (bf16*)out, (size_t)n);
+    const bool vec = n % 4 == 0 && (((uintptr_t)a | (uintptr_t)b | (uintptr_t)out) & 15) == 0;
+    const unsigned blocks = (unsigned)((n / (vec ? 4 : 1) + 255) / 256);
+    if (dtype == VL_F32) {
+        if (vec) return vl_launch(scaled_sum_kernel<float, 4>, dim3(blocks), dim3(256), 0, s, (const float*)a, sa, (const float*)b, sb, (float*)out, (size_t)n);
+        return vl_launch(scaled_sum_kernel<float, 1>, dim3(blocks), dim3(256), 0, s, (const float*)a, sa, (const float*)b, sb, (float*)out, (size_t)n);
+    }
+    if (dtype == VL_BF16) {
+        if (vec) return vl_launch(scaled_sum_kernel<bf16, 4>, dim3(blocks), dim3(256), 0, s, (const bf16*)a, sa, (const bf16*)b, sb, (bf16*)out, (size_t)n);
+        return vl_launch(scaled_sum_kernel<bf16, 1>, dim3(blocks), dim3(256), 0, s, (const bf16*)a, sa, (const bf16*)b, sb, (bf16*)out, (size_t)n);
+    }
     return VL_ERR_UNSUPPORTED;
 }
 
 // x[t, i] <- x[t, i] * sigmoid(g[t, gcol + i]) for i < n, element by element in float32 (an output gate on the
 // concatenated heads of an attention; x rows ldx wide, g rows ldg wide).
-template <typename T>
+__device__ __forceinline__ float gate_of(float g) { return 1.0f / (1.0f + expf(-g)); }
+template <typename T, int VEC>
 __global__ void sigmoid_gate_kernel(T* __restrict__ x, int ldx, const T* __restrict__ g, int ldg, int gcol, int n, size_t total) {
     pdl_launch_dependents();
     pdl_wait();
-    const size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x;
+    const size_t idx = ((size_t)blockIdx.x * 256 + threadIdx.x) * VEC;
     if (idx >= total) return;
     const size_t t = idx / n;
     const int i = (int)(idx - t * n);
-    const float gate = 1.0f / (1.0f + expf(-to_f32(g[t * ldg + gcol + i])));
     T* p = x + t * ldx + i;
-    *p = from_f32<T>(to_f32(*p) * gate);
+    const T* q = g + t * ldg + gcol + i;
+    if (VEC == 4) {
+        const float4 v = Quad<T>::load(p), w = Quad<T>::load(q);
+        Quad<T>::store(p, make_float4(v.x * gate_of(w.x), v.y * gate_of(w.y), v.z * gate_of(w.z), v.w * gate_of(w.w)));
+    } else {
+        *p = from_f32<T>(to_f32(*p) * gate_of(to_f32(*q)));
+    }
 }
 
 extern "C" int vl_sigmoid_gate(void* x, int ldx, const void* g, int ldg, int gcol, int dtype, int T, int n, void* stream) {
     if (T <= 0 || n <= 0) return VL_OK;
     if (ldx < n || gcol < 0 || ldg < gcol + n) return VL_ERR_ARGUMENT;
     const size_t total = (size_t)T * n;
-    const unsigned blocks = (unsigned)((total + 255) / 256);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == VL_F32) return vl_launch(sigmoid_gate_kernel<float>, dim3(blocks), dim3(256), 0, s, (float*)x, ldx, (const float*)g, ldg, gcol, n, total);
-    if (dtype == VL_BF16) return vl_launch(sigmoid_gate_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (bf16*)x, ldx, (const bf16*)g, ldg, gcol, n, total);
+    const bool vec = n % 4 == 0 && ldx % 4 == 0 && ldg % 4 == 0 && gcol % 4 == 0 && (((uintptr_t)x | (uintptr_t)g) & 15) == 0;
+    const unsigned blocks = (unsigned)((total / (vec ? 4 : 1) + 255) / 256);
+    if (dtype == VL_F32) {
+        if (vec) return vl_launch(sigmoid_gate_kernel<float, 4>, dim3(blocks), dim3(256), 0, s, (float*)x, ldx, (const float*)g, ldg, gcol, n, total);
+        return vl_launch(sigmoid_gate_kernel<float, 1>, dim3(blocks), dim3(256), 0, s, (float*)x, ldx, (const float*)g, ldg, gcol, n, total);
+    }
+    if (dtype == VL_BF16) {
+        if (vec) return vl_launch(sigmoid_gate_kernel<bf16, 4>, dim3(blocks), dim3(256), 0, s, (bf16*)x, ldx, (const bf16*)g, ldg, gcol, n, total);
+        return vl_launch(sigmoid_gate_kernel<bf16, 1>, dim3(blocks), dim3(256), 0, s, (bf16*)x, ldx, (const bf16*)g, ldg, gcol, n, total);
+    }
     return VL_ERR_UNSUPPORTED;
 }
