@@ -931,7 +931,7 @@ def puturax_bench(args):
     row = -(-(KR + R) // 16) * 16
     roof = {}
     roof["attention_prefill_tflops"] = {
-        "puturax capped, distance bias, sink (mma.sync)": tf(n_par * 4.0 * H * D * keys_all, us(px, "kernels_prefill", shaped)),
+        "puturax capped, distance bias, sink": tf(n_par * 4.0 * H * D * keys_all, us(px, "kernels_prefill", shaped)),
         "puturax latent row": tf(n_lat * 4.0 * H * row * keys_all, us(px, "kernels_prefill", att)),
         "qwen3": tf(layers * 4.0 * H * D * keys_all, us(q, "kernels_prefill", att)),
         "us_a_layer": {"puturax shaped": round(us(px, "kernels_prefill", shaped) / max(n_par, 1), 1),

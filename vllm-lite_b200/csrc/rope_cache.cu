@@ -474,9 +474,12 @@ extern "C" int vl_conv_rows_norm_rope_write(const void* proj, int pld, const flo
 // cache slot.  Heads lie in rows as [q (nq) | k (nkv) | v (nkv)], each `hd` features wide; the means run over
 // the first `qk_dim` / `v_dim` features (what lies behind them in a padded head is zero and stays zero).
 // A warp per (token, head), the head in registers; sums and factors in float32.  hd up to ROPE_MAX_HD.
+// VEC = 4: a lane holds groups of four neighbouring features (8- or 16-byte accesses), when heads and rows start on such
+// boundaries; the sum of squares then runs over the same values in another order of lanes, which changes no kernel of a
+// model: the launcher's choice depends on sizes and addresses alone.
 // ---------------------------------------------------------------------------------------------------------
 #define HEADNORM_PER_LANE (ROPE_MAX_HD / 32)
-template <typename T>
+template <typename T, int VEC>
 __global__ void __launch_bounds__(ROPE_THREADS)
 head_norm_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ slots,
                        const float* __restrict__ qw, const float* __restrict__ kw, float eps, int qk_dim, int v_norm,
@@ -506,10 +509,16 @@ head_norm_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions, c
     float v[HEADNORM_PER_LANE];
     float ss = 0.f;
 #pragma unroll
-    for (int k = 0; k < HEADNORM_PER_LANE; ++k) {
-        const int i = lane + 32 * k;
-        v[k] = i < hd ? to_f32(src[i]) : 0.f;
-        ss += v[k] * v[k];
+    for (int k = 0; k < HEADNORM_PER_LANE; k += VEC) {
+        const int i = VEC * lane + 32 * k;                            // VEC = 1: lane + 32 k
+        if (VEC == 4) {
+            const float4 q = i < hd ? Quad<T>::load(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            v[k] = q.x; v[k + 1] = q.y; v[k + 2] = q.z; v[k + 3] = q.w;
+            ss += q.x * q.x + q.y * q.y + q.z * q.z + q.w * q.w;
+        } else {
+            v[k] = i < hd ? to_f32(src[i]) : 0.f;
+            ss += v[k] * v[k];
+        }
     }
     float f = 1.f;
     const bool normed = is_q || is_k ? qk_dim > 0 : v_norm != 0;
@@ -520,9 +529,16 @@ head_norm_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions, c
     if (is_q && temp_every > 0 && pos >= 0) f *= 1.0f + temp_coef * logf((float)((pos + 1) / temp_every + 1));
     const float* w = is_q ? qw : (is_k ? kw : nullptr);
 #pragma unroll
-    for (int k = 0; k < HEADNORM_PER_LANE; ++k) {
-        const int i = lane + 32 * k;
-        if (i < hd) dst[i] = from_f32<T>(w ? v[k] * f * w[i] : v[k] * f);
+    for (int k = 0; k < HEADNORM_PER_LANE; k += VEC) {
+        const int i = VEC * lane + 32 * k;
+        if (i >= hd) continue;
+        if (VEC == 4) {
+            float4 q = make_float4(v[k] * f, v[k + 1] * f, v[k + 2] * f, v[k + 3] * f);
+            if (w) { q.x *= w[i]; q.y *= w[i + 1]; q.z *= w[i + 2]; q.w *= w[i + 3]; }
+            Quad<T>::store(dst + i, q);
+        } else {
+            dst[i] = from_f32<T>(w ? v[k] * f * w[i] : v[k] * f);
+        }
     }
 }
 
@@ -537,13 +553,13 @@ extern "C" int vl_head_norm_write(void* qkv, int dtype, const int* positions, co
     const int nheads = nq + 2 * nkv, per = ROPE_THREADS / 32;
     dim3 grid(T, (nheads + per - 1) / per);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == VL_F32)
-        return vl_launch(head_norm_write_kernel<float>, grid, dim3(ROPE_THREADS), 0, s, (float*)qkv, positions, slots, qw, kw, eps,
-                         qk_dim, v_norm, v_dim, v_eps, temp_coef, temp_every, (float*)kcache, (float*)vcache, nq, nkv, hd, page_size,
-                         num_slots, row_stride, err);
-    if (dtype == VL_BF16)
-        return vl_launch(head_norm_write_kernel<bf16>, grid, dim3(ROPE_THREADS), 0, s, (bf16*)qkv, positions, slots, qw, kw, eps,
-                         qk_dim, v_norm, v_dim, v_eps, temp_coef, temp_every, (bf16*)kcache, (bf16*)vcache, nq, nkv, hd, page_size,
-                         num_slots, row_stride, err);
+    const bool vec = hd % 4 == 0 && row_stride % 4 == 0 && (((uintptr_t)qkv | (uintptr_t)kcache | (uintptr_t)vcache) & 15) == 0;
+#define HNW_LAUNCH(TYPE, VEC)                                                                                                    \
+    return vl_launch(head_norm_write_kernel<TYPE, VEC>, grid, dim3(ROPE_THREADS), 0, s, (TYPE*)qkv, positions, slots, qw, kw, eps, \
+                     qk_dim, v_norm, v_dim, v_eps, temp_coef, temp_every, (TYPE*)kcache, (TYPE*)vcache, nq, nkv, hd, page_size,   \
+                     num_slots, row_stride, err)
+    if (dtype == VL_F32) { if (vec) HNW_LAUNCH(float, 4); HNW_LAUNCH(float, 1); }
+    if (dtype == VL_BF16) { if (vec) HNW_LAUNCH(bf16, 4); HNW_LAUNCH(bf16, 1); }
+#undef HNW_LAUNCH
     return VL_ERR_UNSUPPORTED;
 }
