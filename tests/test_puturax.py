@@ -392,6 +392,21 @@ def test_norm_with_a_weight_around_zero_before_and_after_a_sublayer(dtype, W):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("W", [6, 72, 300, 2048, 5000])
+def test_norm_after_two_mixers_side_by_side(dtype, W):
+    """The norm after a sub-layer given the two results of mixers side by side and their factors: it norms
+    s1 a + s2 b (float32, never rounded to the model's dtype) and adds the result into the stream."""
+    w = rand((W,), 30) * 0.3 + 1.0
+    a, b = rand((7, W), 31, dtype, 2.0), rand((7, W), 32, dtype, 0.5)
+    x = rand((7, W), 33, torch.float32, 3.0)
+    y = 0.8 * a.double().cpu() - 1.7 * b.double().cpu()
+    want = x.double().cpu() + P.unit_rms(y, 1e-5) * w.double().cpu()
+    ops().rmsnorm_add(a, w, 1e-5, 1.0, x, pair=(b, 0.8, -1.7))
+    close(x, want, torch.float32, "norm of a pair", tol=3e-6)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("pad", [3, 4])
 @pytest.mark.parametrize("W", [5, 64, 300])
 def test_five_token_shifts_keep_the_row_before(dtype, W, pad):

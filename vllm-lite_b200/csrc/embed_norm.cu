@@ -269,18 +269,23 @@ extern "C" int vl_layernorm_rows(const float* x, const int* rows, const float* w
 template <typename TA>
 __global__ void __launch_bounds__(256)
 rmsnorm_add_kernel(const TA* __restrict__ y, const float* __restrict__ bias, const float* __restrict__ w, float eps, float mult,
-                   float* __restrict__ x, TA* __restrict__ cast, int H) {
+                   float* __restrict__ x, TA* __restrict__ cast, int H, const TA* __restrict__ y2, float s1, float s2) {
     __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
     const int r = blockIdx.x;
     const TA* yr = y + (size_t)r * H;
+    const TA* y2r = y2 ? y2 + (size_t)r * H : nullptr;          // the normed row is s1 * y + s2 * y2 (two sub-layers side by side)
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += 256) { const float d = to_f32(yr[i]) + (bias ? bias[i] : 0.f); ss += d * d; }
+    for (int i = threadIdx.x; i < H; i += 256) {
+        const float d = (y2r ? s1 * to_f32(yr[i]) + s2 * to_f32(y2r[i]) : to_f32(yr[i])) + (bias ? bias[i] : 0.f);
+        ss += d * d;
+    }
     const float inv = 1.0f / sqrtf(block_sum<256>(ss, scratch) / (float)H + eps);
     float* xr = x + (size_t)r * H;
     for (int i = threadIdx.x; i < H; i += 256) {
-        const float v = xr[i] + mult * ((to_f32(yr[i]) + (bias ? bias[i] : 0.f)) * inv * w[i]);
+        const float d = (y2r ? s1 * to_f32(yr[i]) + s2 * to_f32(y2r[i]) : to_f32(yr[i])) + (bias ? bias[i] : 0.f);
+        const float v = xr[i] + mult * (d * inv * w[i]);
         xr[i] = v;
         if (cast) cast[(size_t)r * H + i] = from_f32<TA>(v);
     }
@@ -289,12 +294,13 @@ rmsnorm_add_kernel(const TA* __restrict__ y, const float* __restrict__ bias, con
 template <typename TA, int VPT>
 __global__ void __launch_bounds__(256)
 rmsnorm_add_vec_kernel(const TA* __restrict__ y, const float* __restrict__ bias, const float* __restrict__ w, float eps, float mult,
-                       float* __restrict__ x, TA* __restrict__ cast, int H) {
+                       float* __restrict__ x, TA* __restrict__ cast, int H, const TA* __restrict__ y2, float s1, float s2) {
     __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
     const int r = blockIdx.x, H4 = H >> 2;
     const TA* yr = y + (size_t)r * H;
+    const TA* y2r = y2 ? y2 + (size_t)r * H : nullptr;          // the normed row is s1 * y + s2 * y2
     float4 v[VPT];
     float ss = 0.f;
 #pragma unroll
@@ -302,6 +308,11 @@ rmsnorm_add_vec_kernel(const TA* __restrict__ y, const float* __restrict__ bias,
         const int c = threadIdx.x + 256 * i;
         if (c < H4) {
             v[i] = Quad<TA>::load(yr + 4 * c);
+            if (y2r) {
+                const float4 u = Quad<TA>::load(y2r + 4 * c);
+                v[i].x = s1 * v[i].x + s2 * u.x; v[i].y = s1 * v[i].y + s2 * u.y;
+                v[i].z = s1 * v[i].z + s2 * u.z; v[i].w = s1 * v[i].w + s2 * u.w;
+            }
             if (bias) {
                 const float4 b = Quad<float>::load(bias + 4 * c);
                 v[i].x += b.x; v[i].y += b.y; v[i].z += b.z; v[i].w += b.w;
@@ -326,22 +337,23 @@ rmsnorm_add_vec_kernel(const TA* __restrict__ y, const float* __restrict__ bias,
 }
 
 template <typename TA>
-static int launch_rmsnorm_add(const TA* y, const float* bias, const float* w, float eps, float mult, float* x, TA* cast, int R, int H, cudaStream_t s) {
+static int launch_rmsnorm_add(const TA* y, const float* bias, const float* w, float eps, float mult, float* x, TA* cast, int R, int H,
+                              const TA* y2, float s1, float s2, cudaStream_t s) {
     const int pieces = (H / 4 + 255) / 256;
-    if (H % 4 == 0 && pieces <= 1) return vl_launch(rmsnorm_add_vec_kernel<TA, 1>, dim3(R), dim3(256), 0, s, y, bias, w, eps, mult, x, cast, H);
-    if (H % 4 == 0 && pieces <= 2) return vl_launch(rmsnorm_add_vec_kernel<TA, 2>, dim3(R), dim3(256), 0, s, y, bias, w, eps, mult, x, cast, H);
-    if (H % 4 == 0 && pieces <= 4) return vl_launch(rmsnorm_add_vec_kernel<TA, 4>, dim3(R), dim3(256), 0, s, y, bias, w, eps, mult, x, cast, H);
-    if (H % 4 == 0 && pieces <= 8) return vl_launch(rmsnorm_add_vec_kernel<TA, 8>, dim3(R), dim3(256), 0, s, y, bias, w, eps, mult, x, cast, H);
-    return vl_launch(rmsnorm_add_kernel<TA>, dim3(R), dim3(256), 0, s, y, bias, w, eps, mult, x, cast, H);
+    if (H % 4 == 0 && pieces <= 1) return vl_launch(rmsnorm_add_vec_kernel<TA, 1>, dim3(R), dim3(256), 0, s, y, bias, w, eps, mult, x, cast, H, y2, s1, s2);
+    if (H % 4 == 0 && pieces <= 2) return vl_launch(rmsnorm_add_vec_kernel<TA, 2>, dim3(R), dim3(256), 0, s, y, bias, w, eps, mult, x, cast, H, y2, s1, s2);
+    if (H % 4 == 0 && pieces <= 4) return vl_launch(rmsnorm_add_vec_kernel<TA, 4>, dim3(R), dim3(256), 0, s, y, bias, w, eps, mult, x, cast, H, y2, s1, s2);
+    if (H % 4 == 0 && pieces <= 8) return vl_launch(rmsnorm_add_vec_kernel<TA, 8>, dim3(R), dim3(256), 0, s, y, bias, w, eps, mult, x, cast, H, y2, s1, s2);
+    return vl_launch(rmsnorm_add_kernel<TA>, dim3(R), dim3(256), 0, s, y, bias, w, eps, mult, x, cast, H, y2, s1, s2);
 }
 
 extern "C" int vl_rmsnorm_add(const void* y, int act_dtype, const float* bias, const float* w, float eps, float mult, float* x, void* cast,
-                              int R, int H, void* stream) {
+                              int R, int H, const void* y2, float s1, float s2, void* stream) {
     if (R <= 0) return VL_OK;
     if (H <= 0) return VL_ERR_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
-    if (act_dtype == VL_F32) return launch_rmsnorm_add<float>((const float*)y, bias, w, eps, mult, x, (float*)cast, R, H, s);
-    if (act_dtype == VL_BF16) return launch_rmsnorm_add<bf16>((const bf16*)y, bias, w, eps, mult, x, (bf16*)cast, R, H, s);
+    if (act_dtype == VL_F32) return launch_rmsnorm_add<float>((const float*)y, bias, w, eps, mult, x, (float*)cast, R, H, (const float*)y2, s1, s2, s);
+    if (act_dtype == VL_BF16) return launch_rmsnorm_add<bf16>((const bf16*)y, bias, w, eps, mult, x, (bf16*)cast, R, H, (const bf16*)y2, s1, s2, s);
     return VL_ERR_UNSUPPORTED;
 }
 

@@ -16,7 +16,7 @@
 //                   on it: a row's arithmetic does not depend on its place.
 //   vl_moe_gather   rows[r] = weight(pair) * h[token(pair)] (or h itself), zeros for padding rows
 //   vl_moe_combine  out[t] = sum over the token's choices, in the order of the choices, of
-//                   (weight *) result[place[pair]]
+//                   (weight *) result[place[pair]] (+ add[t]: a row that every token gets, added last)
 //
 // Padded tokens of a graph step are ordinary rows here: they cost a row of work and nobody reads
 // their result.
@@ -199,7 +199,7 @@ __global__ void moe_gather_kernel(const T* __restrict__ h, const int* __restrict
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ result, const int* __restrict__ place,
                                    const float* __restrict__ weights, int top, int N, int scale_output,
-                                   T* __restrict__ out) {
+                                   T* __restrict__ out, const T* __restrict__ add) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -215,6 +215,12 @@ __global__ void moe_combine_kernel(const T* __restrict__ result, const int* __re
 #pragma unroll
                 for (int i = 0; i < 8; ++i) acc[i] += scale_output ? w * v[i] : v[i];
             }
+            if (add) {                                       // one more row for every token (an expert that all tokens share)
+                float v[8];
+                load8(add + (size_t)t * N + n, v);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] += v[i];
+            }
             store8(out + (size_t)t * N + n, acc);
         }
         return;
@@ -227,6 +233,7 @@ __global__ void moe_combine_kernel(const T* __restrict__ result, const int* __re
             const float v = to_f32(result[(size_t)r * N + n]);
             acc += scale_output ? weights[(size_t)t * top + j] * v : v;
         }
+        if (add) acc += to_f32(add[(size_t)t * N + n]);
         out[(size_t)t * N + n] = from_f32<T>(acc);
     }
 }
@@ -270,15 +277,15 @@ extern "C" int vl_moe_gather(const void* h, int dtype, const int* sorted_rows, c
 }
 
 extern "C" int vl_moe_combine(const void* result, int dtype, const int* place, const float* weights, int T, int top,
-                              int N, int scale_output, void* out, void* stream) {
+                              int N, int scale_output, void* out, const void* add, void* stream) {
     if (T <= 0) return VL_OK;
     if (top <= 0 || N <= 0) return VL_ERR_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VL_F32)
         return vl_launch(moe_combine_kernel<float>, dim3(T, (N + 511) / 512), dim3(128), 0, s, (const float*)result, place, weights, top, N,
-                         scale_output, (float*)out);
+                         scale_output, (float*)out, (const float*)add);
     if (dtype == VL_BF16)
         return vl_launch(moe_combine_kernel<bf16>, dim3(T, (N + 511) / 512), dim3(128), 0, s, (const bf16*)result, place, weights, top, N,
-                         scale_output, (bf16*)out);
+                         scale_output, (bf16*)out, (const bf16*)add);
     return VL_ERR_UNSUPPORTED;
 }

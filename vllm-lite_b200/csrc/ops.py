@@ -33,7 +33,8 @@ def dtype_code(dtype) -> int:
 
 _SIGNATURES = {
     ("embed_norm", "vl_embed"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
-    ("embed_norm", "vl_rmsnorm_add"): [c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    ("embed_norm", "vl_rmsnorm_add"): [c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                                       c_float, c_float, c_void_p],
     ("embed_norm", "vl_add_rmsnorm"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     ("embed_norm", "vl_add_bias"): [c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p],
     ("embed_norm", "vl_cast"): [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p],
@@ -108,7 +109,7 @@ _SIGNATURES = {
                                                        c_void_p, c_int, c_float, c_float, c_float, c_void_p, c_void_p],
     ("moe", "vl_moe_align"): [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     ("moe", "vl_moe_gather"): [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
-    ("moe", "vl_moe_combine"): [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    ("moe", "vl_moe_combine"): [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
     ("gemm_f32", "vl_gemm_f32_nt"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     ("gemm_bf16", "vl_gemm_bf16_small_m"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                             c_void_p, c_int, c_void_p],
@@ -842,9 +843,15 @@ def layernorm_add(y, weight, eps, x, cast=None):
     return x
 
 
-def rmsnorm_add(y, weight, eps, mult, x, cast=None, bias=None):
+def rmsnorm_add(y, weight, eps, mult, x, cast=None, bias=None, pair=None):
     """x[r] += mult * (y[r] / sqrt(mean(y[r]^2) + eps) * weight), x float32 [R, H], y in the activation dtype; `cast`
-    (same dtype as y, or None) receives the new x.  `bias` (float32 [H] or None) is added to every row of y first."""
+    (same dtype as y, or None) receives the new x.  `bias` (float32 [H] or None) is added to every row of y first.
+    `pair` = (y2, s1, s2): the normed row is s1 * y + s2 * y2 (the results of two sub-layers side by side), in float32."""
+    y2, s1, s2 = pair if pair is not None else (None, 1.0, 0.0)
+    if y2 is not None:
+        _need(y2, y.dtype, "y2", 2)
+        if y2.shape != y.shape:
+            raise KernelError("rmsnorm_add: the two rows of a pair have one shape")
     _need(y, None, "y", 2); _need(x, torch.float32, "x", 2); _need(weight, torch.float32, "weight", 1)
     if y.shape != x.shape or weight.shape[0] != x.shape[1]:
         raise KernelError(f"rmsnorm_add: y {tuple(y.shape)}, x {tuple(x.shape)}, weight {tuple(weight.shape)}")
@@ -857,7 +864,8 @@ def rmsnorm_add(y, weight, eps, mult, x, cast=None, bias=None):
         if bias.shape[0] != x.shape[1]:
             raise KernelError("rmsnorm_add: the bias has one entry per column")
     _check(_fn("embed_norm", "vl_rmsnorm_add")(_ptr(y), dtype_code(y.dtype), _ptr(bias), _ptr(weight), float(eps), float(mult), _ptr(x),
-                                               _ptr(cast), x.shape[0], x.shape[1], _stream()), "vl_rmsnorm_add")
+                                               _ptr(cast), x.shape[0], x.shape[1], _ptr(y2), float(s1), float(s2), _stream()),
+           "vl_rmsnorm_add")
     return x
 
 
@@ -1127,13 +1135,19 @@ def moe_gather(h, sorted_rows, weights, top, rows, scale_input):
     return rows
 
 
-def moe_combine(result, place, weights, top, out, scale_output):
+def moe_combine(result, place, weights, top, out, scale_output, add=None):
+    """out[t] = the sum over token t's choices (in their order) of (weight *) result[place[t, j]]; `add` [T, N]: one more
+    row per token, added last (a feed-forward that every token passes)."""
     _need(result, None, "result", 2); _need(out, result.dtype, "out", 2); _need(weights, torch.float32, "weights")
     T, N = out.shape
     if result.shape[1] != N or place.shape[0] < T * top:
         raise KernelError("moe_combine: shapes disagree")
+    if add is not None:
+        _need(add, out.dtype, "add", 2)
+        if add.shape != out.shape:
+            raise KernelError("moe_combine: the added rows have the output's shape")
     _check(_fn("moe", "vl_moe_combine")(_ptr(result), dtype_code(result.dtype), _ptr(place), _ptr(weights), T, int(top), N,
-                                        int(bool(scale_output)), _ptr(out), _stream()), "vl_moe_combine")
+                                        int(bool(scale_output)), _ptr(out), _ptr(add), _stream()), "vl_moe_combine")
     return out
 
 

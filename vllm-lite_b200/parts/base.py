@@ -170,6 +170,16 @@ class StreamSink:
     size: int
 
 
+@dataclass
+class ScaledPair:
+    """The results of two sub-layers side by side, not yet added: the sum is a_scale * a + b_scale * b.  A mixer that says
+    `returns_pair` hands this to a block whose next norm says `takes_pair`; the norm's kernel forms the sum as it reads."""
+    a: torch.Tensor
+    a_scale: float
+    b: torch.Tensor
+    b_scale: float
+
+
 def sub_weights(weights: dict, prefix: str) -> dict:
     n = len(prefix)
     return {k[n:]: v for k, v in weights.items() if k.startswith(prefix)}

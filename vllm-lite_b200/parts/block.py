@@ -206,7 +206,10 @@ class SandwichBlock:
         h = self.norm1(residual.x, residual.pending, step, tag="norm1")
         residual.pending = None
         residual.cast = None
-        y = self.mixer(h, step, cache)
+        if getattr(self.mixer, "returns_pair", False) and getattr(self.post1, "takes_pair", False):
+            y = self.mixer(h, step, cache, as_pair=True)          # two mixers side by side: the norm's kernel adds them as it reads
+        else:
+            y = self.mixer(h, step, cache)
         self.post1.add_normed(y, residual.x, step, None)
         if self.ffn is not None:
             h = self.norm2(residual.x, None, step, tag="norm2")

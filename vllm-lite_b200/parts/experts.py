@@ -133,8 +133,8 @@ class RoutedExperts:
             ops.gemm_grouped_tc5(rows, self.gate_up, act, tile_group, step.err, sorted_rows,
                                  weights if s.scale_input else None, s.activation, s.alpha, s.limit, s.up_shift)
             res = ops.gemm_grouped_tc5(act, self.down, ws.get(tag + "moe.down", (cap, H), self.dtype), tile_group, step.err)
-            out = ops.moe_combine(res, place, weights, top, ws.get(tag + "moe.out", (T, H), self.dtype), not s.scale_input)
-            return self._add_shared(out, h, step)
+            return ops.moe_combine(res, place, weights, top, ws.get(tag + "moe.out", (T, H), self.dtype), not s.scale_input,
+                                   add=self._shared(h, step))
         if self.fused:
             ops.gemm_grouped_fused(h, self.gate_up, act, tile_group, bm, sorted_rows, top,
                                    weights if s.scale_input else None, s.activation, s.alpha, s.limit, s.up_shift)
@@ -147,10 +147,8 @@ class RoutedExperts:
                 ops.unary_act(gu, act, s.activation)
         res = ops.gemm_grouped(act, self.down, ws.get(tag + "moe.down", (cap, H), self.dtype), tile_group, bm)
         out = ws.get(tag + "moe.out", (T, H), self.dtype)
-        return self._add_shared(ops.moe_combine(res, place, weights, top, out, not s.scale_input), h, step)
+        return ops.moe_combine(res, place, weights, top, out, not s.scale_input, add=self._shared(h, step))
 
-    def _add_shared(self, out, h, step):
-        if self.shared is None:
-            return out
-        from ..csrc import ops
-        return ops.scaled_sum(out, 1.0, self.shared(h, step), 1.0, out)
+    def _shared(self, h, step):
+        """The shared feed-forward's rows (None without one): the kernel that sums a token's choices adds them last."""
+        return None if self.shared is None else self.shared(h, step)

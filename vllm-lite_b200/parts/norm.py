@@ -35,12 +35,17 @@ class RmsNorm:
         self.weight = (w.reshape(1).expand(spec.size) if spec.scalar else w).contiguous()
 
     adds_bias = True           # add_normed takes the bias that the sub-layer's last product left out
+    takes_pair = True          # ... and a `ScaledPair` (two sub-layers side by side) in place of y
 
     def add_normed(self, y, x, step, cast=None, mult=1.0, bias=None):
         """x += mult * norm(y + bias): what a block that norms its sub-layers' OUTPUTS calls; `cast` (a buffer in the
-        activation dtype, or None) receives the new x.  Returns cast."""
+        activation dtype, or None) receives the new x.  y may be a `ScaledPair`.  Returns cast."""
         from ..csrc import ops
-        ops.rmsnorm_add(y, self.weight, self.spec.eps, mult, x, cast, bias=bias)
+        from .base import ScaledPair
+        if isinstance(y, ScaledPair):
+            ops.rmsnorm_add(y.a, self.weight, self.spec.eps, mult, x, cast, bias=bias, pair=(y.b, y.a_scale, y.b_scale))
+        else:
+            ops.rmsnorm_add(y, self.weight, self.spec.eps, mult, x, cast, bias=bias)
         return cast
 
     def fused_rms(self):
