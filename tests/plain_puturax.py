@@ -92,7 +92,7 @@ def distance_bias(r1, r2, dist):
 
 
 def softmax_plus_one(s):
-    """exp(s_j) / (1 + sum exp(s)): a sink with score 0 and no value."""
+    """exp(s_j) / (1 + sum exp(s)): the denominator holds one more term, e^0, that brings no value row."""
     mx = torch.clamp(s.max(), min=0.0)
     e = torch.exp(s - mx)
     return e / (torch.exp(-mx) + e.sum())

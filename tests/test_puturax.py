@@ -291,8 +291,8 @@ def test_plain_pieces_behave():
     one = torch.ones(3, 1, dtype=torch.float64)
     o = P.decayed_memory(one, one, one, 0.5 * one, torch.tensor([3.0], dtype=torch.float64))
     assert torch.allclose(o[:, 0], torch.tensor([3.0, 4.0, 4.5], dtype=torch.float64))
-    # choice by score + correction inside the kept groups; weights without the correction; masked experts are minus
-    # infinity, not 0 (every choice score here is negative)
+    # choice by score + correction inside the kept groups; weights without the correction; every choice score here is
+    # negative, so an expert outside the kept groups would win if it were masked with a zero
     h = torch.eye(4, dtype=torch.float64)[:1]
     router = torch.tensor([[0.0, 0, 0, 0], [2.0, 0, 0, 0], [1.0, 0, 0, 0], [-1.0, 0, 0, 0]])
     corr = torch.tensor([-3.0, -5.0, -2.0, -2.5])
@@ -689,8 +689,8 @@ def test_tcgen05_prompt_kernel_takes_the_cap_the_distance_bias_and_the_sink(H_, 
 @pytest.mark.gpu
 @pytest.mark.parametrize("E,top,groups,keep", [(8, 2, 4, 2), (16, 4, 4, 3), (6, 6, 1, 1), (6, 1, 6, 1), (12, 3, 3, 2), (5, 2, 5, 3), (9, 3, 3, 1)])
 def test_choice_by_score_plus_correction_within_the_best_groups(E, top, groups, keep):
-    """Negative corrections (every choice score below zero: a masked expert must count as minus infinity, not 0), groups
-    that count by their two best, weights from the scores alone, divided by their sum."""
+    """Negative corrections, so that every choice score lies below zero: an expert outside the kept groups must never win, as it
+    would if it were masked with a zero; groups that count by their two best; weights from the scores alone, over their sum."""
     o = ops()
     T, K = 64, 32
     h = rand((T, K), 90, torch.float32)
